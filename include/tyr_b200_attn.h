@@ -1,0 +1,169 @@
+/*
+ * tyr_b200_attn.h — C ABI of the B200 (sm_100a) attention operator.
+ *
+ * Drop-in boundary for Tyr's typed attention call.  Every entry point takes
+ * plain pointers and sizes (no torch / ATen / Lean types), launches on the
+ * stream the caller passes (a cudaStream_t cast to void*, exactly the value
+ * Tyr's `torch.cuda_current_stream` hands to its generated launchers,
+ * cc/src/tyr.cpp:4314-4331) and never synchronises the device unless the
+ * entry point is documented as a host-buffer call.
+ *
+ * Return value of every `int` function: 0 = ok; negative = TYR_ATTN_ERR_*
+ * (argument rejected before any launch); positive = a cudaError_t raised by
+ * the launch itself.  tyr_b200_attn_strerror() turns either into text for the
+ * IO error string Tyr's launchers return (Tyr/GPU/Codegen/Attribute.lean:376-385).
+ *
+ * All tensors are row-major with unit stride on the head dimension.
+ * Strides are in ELEMENTS.  bf16 tensors must be 16-byte aligned with strides
+ * that are multiples of 8 elements (TMA requirement).
+ */
+#ifndef TYR_B200_ATTN_H_
+#define TYR_B200_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TYR_ATTN_ABI_VERSION 1
+
+/* element types of Q/K/V/O */
+#define TYR_ATTN_BF16 0
+#define TYR_ATTN_F32 1 /* accepted only with check_mode = 1 */
+
+/* argument errors (returned negated: -TYR_ATTN_ERR_x) */
+#define TYR_ATTN_ERR_NULL 1        /* a required pointer is NULL */
+#define TYR_ATTN_ERR_SHAPE 2       /* a size is zero/negative or n_head % n_kv_head != 0 */
+#define TYR_ATTN_ERR_HEAD_DIM 3    /* head_dim not in {64,128} (tensor-core path) */
+#define TYR_ATTN_ERR_ALIGN 4       /* pointer or stride breaks the 16-byte rule */
+#define TYR_ATTN_ERR_DTYPE 5       /* dtype/check_mode combination not supported */
+#define TYR_ATTN_ERR_DROPOUT 6     /* dropout_p != 0: caller keeps its LibTorch path */
+#define TYR_ATTN_ERR_WORKSPACE 7   /* workspace missing or too small */
+#define TYR_ATTN_ERR_NO_DEVICE 8   /* no sm_100 device / driver entry point missing */
+#define TYR_ATTN_ERR_DEVICE_WAIT 9 /* a bounded in-kernel wait gave up (see tyr_b200_attn_device_status) */
+#define TYR_ATTN_ERR_TOO_LARGE 10  /* size beyond a documented maximum */
+
+/* ------------------------------------------------------------------------
+ * Prefill: O = softmax(Q K^T * scale + causal) V, per-row LSE.
+ *
+ * Raw-pointer form of Tyr's generated launcher ABI (caller-allocated outputs,
+ * explicit stream; Tyr/GPU/Codegen/Attribute.lean:331-386 and the launch at
+ * Examples/GPU/RunFlashAttn.lean:81).  Q head h reads KV head h / (n_head /
+ * n_kv_head), the map `repeat_interleave` produces in cc/src/tyr.cpp:3931-3938.
+ * `is_causal` masks key j for query i when j > i (top-left aligned, as ATen and
+ * cc/src/tyr.cpp:3990-3991).  LSE is the natural log of the sum of exp of the
+ * SCALED scores (Tyr/GPU/Codegen/Macros.lean:155-163).
+ * ---------------------------------------------------------------------- */
+typedef struct TyrAttnPrefillArgs {
+  const void* q; /* [batch, n_head,    q_seq,  head_dim] */
+  const void* k; /* [batch, n_kv_head, kv_seq, head_dim] */
+  const void* v; /* [batch, n_kv_head, kv_seq, head_dim] */
+  void* o;       /* [batch, n_head,    q_seq,  head_dim], same dtype as q */
+  float* lse;    /* [batch, n_head, q_seq] fp32 contiguous, or NULL */
+  int32_t batch, n_head, n_kv_head, q_seq, kv_seq, head_dim;
+  int64_t q_stride[3]; /* elements: batch, head, seq */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int32_t dtype;      /* TYR_ATTN_BF16 | TYR_ATTN_F32 */
+  int32_t is_causal;  /* 0 | 1 */
+  float scale;        /* 0 => 1/sqrt(head_dim), ATen's default */
+  int32_t check_mode; /* 1 => fp32-FMA kernel (no tensor cores), any head_dim <= 256 */
+} TyrAttnPrefillArgs;
+
+int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* args, void* stream);
+
+/* Contiguous-layout forms whose argument lists mirror the Lean externs one to
+ * one: tensor handles become device pointers, the result tensor becomes the
+ * caller-allocated `out`, and the stream is explicit.  bf16 only.
+ *   tyr_b200_sdpa_4d       <- lean_torch_sdpa_4d       cc/src/tyr.cpp:2563-2589
+ *   tyr_b200_sdpa_gqa      <- lean_torch_sdpa_gqa      cc/src/tyr.cpp:3913-3949
+ *   tyr_b200_sdpa_gqa_qkv  <- lean_torch_sdpa_gqa_qkv  cc/src/tyr.cpp:4100-4133
+ * With enable_gqa = 0 the reference passes K/V through unchanged, which ATen
+ * only accepts when n_head == n_kv_head; the same rule is enforced here. */
+int tyr_b200_sdpa_4d(uint64_t batch, uint64_t n_head, uint64_t seq, uint64_t head_dim,
+                     const void* q, const void* k, const void* v, void* out,
+                     double dropout_p, uint8_t is_causal, void* stream);
+int tyr_b200_sdpa_gqa(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                      uint64_t head_dim, const void* q, const void* k, const void* v, void* out,
+                      double dropout_p, uint8_t is_causal, uint8_t enable_gqa, void* stream);
+int tyr_b200_sdpa_gqa_qkv(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t q_seq,
+                          uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k,
+                          const void* v, void* out, double dropout_p, uint8_t is_causal,
+                          uint8_t enable_gqa, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Decode: one query token per sequence over a (possibly ragged) KV cache,
+ * split-KV partial attention followed by an LSE merge.  Replaces the
+ * q_seq = 1, is_causal = false call in QwenAttention.forwardStep
+ * (Tyr/Model/Qwen/Attention.lean:198-200 -> cc/src/tyr.cpp:4100-4133) without
+ * the per-token repeat_interleave of the whole cache.
+ *
+ * Two cache layouts:
+ *  dense : k/v point at [batch, n_kv_head, cap, head_dim] (Tyr's KVCache,
+ *          Attention.lean:54-68); k_stride/v_stride = {batch, head, seq}.
+ *  ragged: k_ptrs/v_ptrs are DEVICE arrays of `batch` device pointers, one
+ *          per sequence, each to [n_kv_head, len_b, head_dim] with seq stride
+ *          k_stride[2] and head stride kv_head_strides[b] (or, when that is
+ *          NULL, len_b * k_stride[2] i.e. tightly packed).  k/v are ignored.
+ * kv_lens: DEVICE int32[batch] of valid keys per sequence, or NULL for
+ * max_kv_seq everywhere.  Every length must be in [1, max_kv_seq].
+ * ---------------------------------------------------------------------- */
+typedef struct TyrAttnDecodeArgs {
+  const void* q; /* [batch, n_head, head_dim] */
+  void* o;       /* [batch, n_head, head_dim] */
+  float* lse;    /* [batch, n_head] or NULL */
+  const void* k;
+  const void* v;
+  const void* const* k_ptrs;
+  const void* const* v_ptrs;
+  const int32_t* kv_lens;
+  const int64_t* kv_head_strides;
+  int32_t batch, n_head, n_kv_head, max_kv_seq, head_dim;
+  int64_t q_stride[2]; /* elements: batch, head */
+  int64_t o_stride[2];
+  int64_t k_stride[3]; /* elements: batch, head, seq (ragged: only [2] is read) */
+  int64_t v_stride[3];
+  float scale;        /* 0 => 1/sqrt(head_dim) */
+  int32_t max_splits; /* 0 => 64; clamped to [1,64] */
+  void* workspace;    /* device scratch, >= tyr_b200_attn_decode_workspace_bytes() */
+  size_t workspace_bytes;
+} TyrAttnDecodeArgs;
+
+size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim,
+                                            int32_t max_kv_seq, int32_t max_splits);
+int tyr_b200_attn_decode(const TyrAttnDecodeArgs* args, void* stream);
+
+/* LSE merge of two partial attention results over disjoint key sets (the
+ * reduction Tyr states in ringAttnReduce, Tyr/GPU/Kernels/RingAttn.lean:164-180):
+ *   L = Lr + log(1 + exp(Lb - Lr));  O = Or*exp(Lr-L) + Ob*exp(Lb-L).
+ * o_a/o_b/o_out: fp32 [rows, head_dim]; lse_*: fp32 [rows].  In place allowed. */
+int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                        float* o_out, float* lse_out, int64_t rows, int32_t head_dim, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Host-buffer call: same arithmetic as tyr_b200_attn_prefill, but every
+ * pointer in `args` is HOST memory (pinned or pageable).  Copies Q/K/V to the
+ * device, runs the kernel, copies O (and LSE) back and synchronises.  This is
+ * the call a Tyr build makes when its tensors live on the CPU, which is the
+ * only place the reference's CI ever runs attention
+ * (.github/workflows/ci.yml:12-17).  Device staging buffers are cached per
+ * device and grown on demand.  Tensors must be contiguous.
+ * ---------------------------------------------------------------------- */
+int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* args, int32_t device);
+
+/* Status word the kernels' bounded waits write (0 = none gave up).  Reads the
+ * word with a device synchronise; `clear` != 0 resets it. */
+int tyr_b200_attn_device_status(int32_t device, int32_t clear);
+
+const char* tyr_b200_attn_strerror(int code);
+int tyr_b200_attn_abi_version(void);
+/* number of kernel launches issued by this library since load (all threads) */
+uint64_t tyr_b200_attn_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TYR_B200_ATTN_H_ */

@@ -1,0 +1,185 @@
+/*
+ * attn_oracle.c — CPU restatement of Tyr's attention path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing the product ships may call into this file:
+ * it is the checker for the tests, the smoke check and the CPU-baseline leg of
+ * the benchmark.  The arithmetic of the reference path lives in a third-party
+ * dependency that is not vendored in the reference tree: LibTorch/ATen
+ * `scaled_dot_product_attention` (the reference pins LibTorch 2.9.1 for CPU
+ * builds, Readme.md:37,53 and .github/workflows/ci.yml:12).  This file restates
+ * the published algorithm and is pinned against outputs of that same ATen
+ * operator (torch 2.11 in this image) stored under tests/golden/, and against
+ * closed-form cases.  The reference's own tests hold no golden vectors for
+ * attention (fixtures are generated at run time, Examples/GPU/FixtureRunner.lean:22-39).
+ *
+ * What each function follows:
+ *   tyr_oracle_sdpa        softmax(Q K^T * scale + mask) V on fp32 data, the formula of the
+ *                          reference's fixture generator (Examples/GPU/RunFlashAttn.lean:30-48);
+ *                          GQA head map of repeat_interleave (cc/src/tyr.cpp:3931-3938);
+ *                          causal mask "col > row is masked" (cc/src/tyr.cpp:3990-3991);
+ *                          LSE = log(sum(exp(scaled scores))) (RunFlashAttn.lean:45-48).
+ *   tyr_oracle_sdpa_online the running max / running sum form of
+ *                          Tyr/GPU/Codegen/Macros.lean:121-163 with fp32 state.
+ *   tyr_oracle_merge2      LSE merge of two partial results,
+ *                          Tyr/GPU/Kernels/RingAttn.lean:164-180.
+ *   tyr_oracle_bf16_round  round-to-nearest-even fp32 -> bf16 -> fp32, the quantisation the
+ *                          reference applies to inputs before its fp32 check (RunFlashAttn.lean:30-36).
+ *
+ * Layout: contiguous row-major [B, H, S, D] fp32.  Accumulation is in double, so
+ * the result is the correctly rounded fp32 answer to well below 1e-6 relative.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int tyr_oracle_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+void tyr_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
+void tyr_oracle_bf16_round(const float* in, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    uint32_t u;
+    memcpy(&u, &in[i], 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) {
+      u |= 0x00400000u; /* quiet NaN */
+    } else {
+      u += 0x7fffu + ((u >> 16) & 1u);
+    }
+    u &= 0xffff0000u;
+    memcpy(&out[i], &u, 4);
+  }
+}
+
+/* Direct form.  Returns 0, or -1 on bad arguments. */
+int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, float* lse, int B,
+                    int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0) return -1;
+  const int g = Hq / Hkv; /* query head h reads KV head h / g */
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  int failed = 0;
+#pragma omp parallel
+  {
+    double* s = (double*)malloc(sizeof(double) * (size_t)Skv);
+    double* acc = (double*)malloc(sizeof(double) * (size_t)D);
+    if (!s || !acc) {
+#pragma omp atomic write
+      failed = 1;
+    } else {
+#pragma omp for schedule(dynamic, 16)
+      for (int64_t r = 0; r < rows; ++r) {
+        const int i = (int)(r % Sq);
+        const int h = (int)((r / Sq) % Hq);
+        const int b = (int)(r / ((int64_t)Sq * Hq));
+        const float* qr = q + r * D;
+        const float* kb = k + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
+        const float* vb = v + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
+        const int n = is_causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv; /* keys j <= i */
+        double mx = -INFINITY;
+        for (int j = 0; j < n; ++j) {
+          const float* kr = kb + (int64_t)j * D;
+          double dot = 0.0;
+          for (int d = 0; d < D; ++d) dot += (double)qr[d] * (double)kr[d];
+          s[j] = dot * (double)scale;
+          if (s[j] > mx) mx = s[j];
+        }
+        double sum = 0.0;
+        for (int d = 0; d < D; ++d) acc[d] = 0.0;
+        for (int j = 0; j < n; ++j) {
+          const double p = exp(s[j] - mx);
+          sum += p;
+          const float* vr = vb + (int64_t)j * D;
+          for (int d = 0; d < D; ++d) acc[d] += p * (double)vr[d];
+        }
+        for (int d = 0; d < D; ++d) o[r * D + d] = (float)(acc[d] / sum);
+        if (lse) lse[r] = (float)(mx + log(sum));
+      }
+    }
+    free(s);
+    free(acc);
+  }
+  return failed ? -1 : 0;
+}
+
+/* Online form with fp32 state, keys visited in blocks of `block` (Macros.lean:121-163):
+ *   prevMax = rowMax; rowMax = max(rowMax, max(scores)); scale = exp(prevMax - rowMax);
+ *   out *= scale; rowSum *= scale; scores = exp(scores - rowMax); rowSum += sum(scores);
+ *   out += scores V;  finally out /= rowSum, lse = log(rowSum) + rowMax. */
+int tyr_oracle_sdpa_online(const float* q, const float* k, const float* v, float* o, float* lse,
+                           int B, int Hq, int Hkv, int Sq, int Skv, int D, int is_causal,
+                           float scale, int block) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0 ||
+      block <= 0 || block > 4096)
+    return -1;
+  const int g = Hq / Hkv;
+  const int64_t rows = (int64_t)B * Hq * Sq;
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t r = 0; r < rows; ++r) {
+    const int i = (int)(r % Sq);
+    const int h = (int)((r / Sq) % Hq);
+    const int b = (int)(r / ((int64_t)Sq * Hq));
+    const float* qr = q + r * D;
+    const float* kb = k + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
+    const float* vb = v + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
+    const int n = is_causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv;
+    float row_max = -INFINITY, row_sum = 0.f;
+    float out[1024];
+    float sc[4096];
+    if (D > 1024) continue;
+    for (int d = 0; d < D; ++d) out[d] = 0.f;
+    for (int j0 = 0; j0 < n; j0 += block) {
+      const int nb = (n - j0 < block) ? n - j0 : block;
+      const float prev_max = row_max;
+      for (int j = 0; j < nb; ++j) {
+        const float* kr = kb + (int64_t)(j0 + j) * D;
+        float dot = 0.f;
+        for (int d = 0; d < D; ++d) dot += qr[d] * kr[d];
+        sc[j] = dot * scale;
+        if (sc[j] > row_max) row_max = sc[j];
+      }
+      const float resc = (prev_max == -INFINITY) ? 0.f : expf(prev_max - row_max);
+      for (int d = 0; d < D; ++d) out[d] *= resc;
+      row_sum *= resc;
+      for (int j = 0; j < nb; ++j) {
+        sc[j] = expf(sc[j] - row_max);
+        row_sum += sc[j];
+        const float* vr = vb + (int64_t)(j0 + j) * D;
+        for (int d = 0; d < D; ++d) out[d] += sc[j] * vr[d];
+      }
+    }
+    for (int d = 0; d < D; ++d) o[r * D + d] = out[d] / row_sum;
+    if (lse) lse[r] = logf(row_sum) + row_max;
+  }
+  return 0;
+}
+
+/* L = Lr + log(1 + exp(Lb - Lr));  O = Or*exp(Lr - L) + Ob*exp(Lb - L)
+ * (RingAttn.lean:164-180), evaluated with the larger LSE as Lr so that exp never overflows. */
+void tyr_oracle_merge2(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                       float* o_out, float* lse_out, int64_t rows, int D) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const double la = lse_a[r], lb = lse_b[r];
+    const double hi = la > lb ? la : lb, lo = la > lb ? lb : la;
+    const double L = (hi == -INFINITY) ? -INFINITY : hi + log1p(exp(lo - hi));
+    const double wa = (la == -INFINITY) ? 0.0 : exp(la - L), wb = (lb == -INFINITY) ? 0.0 : exp(lb - L);
+    for (int d = 0; d < D; ++d)
+      o_out[r * D + d] = (float)((double)o_a[r * D + d] * wa + (double)o_b[r * D + d] * wb);
+    lse_out[r] = (float)L;
+  }
+}

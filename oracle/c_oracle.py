@@ -1,0 +1,90 @@
+"""ctypes binding of attn_oracle.c (numpy in, numpy out).  Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libattn_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    src = os.path.join(_HERE, "attn_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "libattn_oracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_SO)
+        f32p = ctypes.POINTER(ctypes.c_float)
+        L.tyr_oracle_sdpa.argtypes = [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 7 + [ctypes.c_float]
+        L.tyr_oracle_sdpa.restype = ctypes.c_int
+        L.tyr_oracle_sdpa_online.argtypes = (
+            [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 7 + [ctypes.c_float, ctypes.c_int]
+        )
+        L.tyr_oracle_sdpa_online.restype = ctypes.c_int
+        L.tyr_oracle_merge2.argtypes = [f32p] * 6 + [ctypes.c_int64, ctypes.c_int]
+        L.tyr_oracle_merge2.restype = None
+        L.tyr_oracle_bf16_round.argtypes = [f32p, f32p, ctypes.c_int64]
+        L.tyr_oracle_bf16_round.restype = None
+        L.tyr_oracle_threads.restype = ctypes.c_int
+        L.tyr_oracle_set_threads.argtypes = [ctypes.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def _c(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def threads() -> int:
+    return int(lib().tyr_oracle_threads())
+
+
+def sdpa(q, k, v, is_causal: bool, scale: float | None = None, online_block: int = 0):
+    """q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] fp32 -> (o [B,Hq,Sq,D], lse [B,Hq,Sq])."""
+    q, k, v = _c(q), _c(k), _c(v)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    assert k.shape == v.shape and k.shape[0] == B and k.shape[3] == D
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(D))
+    o = np.empty_like(q)
+    lse = np.empty((B, Hq, Sq), dtype=np.float32)
+    if online_block:
+        rc = lib().tyr_oracle_sdpa_online(_p(q), _p(k), _p(v), _p(o), _p(lse), B, Hq, Hkv, Sq, Skv, D,
+                                          int(bool(is_causal)), scale, online_block)
+    else:
+        rc = lib().tyr_oracle_sdpa(_p(q), _p(k), _p(v), _p(o), _p(lse), B, Hq, Hkv, Sq, Skv, D,
+                                   int(bool(is_causal)), scale)
+    if rc != 0:
+        raise ValueError("tyr_oracle_sdpa rejected its arguments")
+    return o, lse
+
+
+def merge2(o_a, lse_a, o_b, lse_b):
+    o_a, o_b, lse_a, lse_b = _c(o_a), _c(o_b), _c(lse_a), _c(lse_b)
+    rows, D = lse_a.size, o_a.shape[-1]
+    o = np.empty_like(o_a)
+    lse = np.empty_like(lse_a)
+    lib().tyr_oracle_merge2(_p(o_a), _p(lse_a), _p(o_b), _p(lse_b), _p(o), _p(lse), rows, D)
+    return o, lse
+
+
+def bf16_round(x) -> np.ndarray:
+    x = _c(x)
+    out = np.empty_like(x)
+    lib().tyr_oracle_bf16_round(_p(x), _p(out), x.size)
+    return out

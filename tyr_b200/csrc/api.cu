@@ -1,0 +1,284 @@
+// C ABI of the attention library: argument checks, dispatch to the kernels,
+// the host-buffer call and the per-device status word.  The checks mirror the
+// pre-launch checks of Tyr's generated launchers (is_cuda / is_contiguous /
+// dim <= 4 -> IO error string, Tyr/GPU/Codegen/Attribute.lean:333-336) in
+// raw-pointer terms: non-null, sizes, alignment, dtype.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "attn_internal.h"
+
+namespace tyr {
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;       // guards g_state
+std::mutex g_host_mu;  // serialises the host-buffer call and guards g_stage
+DeviceState g_state[kMaxDevices];
+std::atomic<uint64_t> g_launches{0};
+
+struct HostStage {  // device staging buffers of the host-buffer call, grown on demand
+  void* buf = nullptr;
+  size_t bytes = 0;
+  cudaStream_t stream = nullptr;
+};
+HostStage g_stage[kMaxDevices];
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+float resolve_scale(float scale, int d) { return scale != 0.f ? scale : 1.0f / std::sqrt((float)d); }
+
+int current_device_checked(int* dev) {
+  cudaError_t e = cudaGetDevice(dev);
+  if (e != cudaSuccess) return (int)e;
+  if (*dev < 0 || *dev >= kMaxDevices) return -TYR_ATTN_ERR_NO_DEVICE;
+  return 0;
+}
+
+int check_prefill(const TyrAttnPrefillArgs* a) {
+  if (!a || !a->q || !a->k || !a->v || !a->o) return -TYR_ATTN_ERR_NULL;
+  if (a->batch <= 0 || a->n_head <= 0 || a->n_kv_head <= 0 || a->q_seq <= 0 || a->kv_seq <= 0 ||
+      a->head_dim <= 0)
+    return -TYR_ATTN_ERR_SHAPE;
+  if (a->n_head % a->n_kv_head != 0) return -TYR_ATTN_ERR_SHAPE;
+  if (a->dtype != TYR_ATTN_BF16 && a->dtype != TYR_ATTN_F32) return -TYR_ATTN_ERR_DTYPE;
+  if (a->dtype == TYR_ATTN_F32 && !a->check_mode) return -TYR_ATTN_ERR_DTYPE;
+  if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
+  if (!a->check_mode) {
+    if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
+    if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
+      return -TYR_ATTN_ERR_ALIGN;
+    const int64_t* s[4] = {a->q_stride, a->k_stride, a->v_stride, a->o_stride};
+    const int dims[4][3] = {{a->batch, a->n_head, a->q_seq},
+                            {a->batch, a->n_kv_head, a->kv_seq},
+                            {a->batch, a->n_kv_head, a->kv_seq},
+                            {a->batch, a->n_head, a->q_seq}};
+    for (int t = 0; t < 4; ++t)
+      for (int i = 0; i < 3; ++i)
+        if (dims[t][i] > 1 && (s[t][i] <= 0 || (s[t][i] & 7))) return -TYR_ATTN_ERR_ALIGN;
+  } else if (a->head_dim > 256) {
+    return -TYR_ATTN_ERR_HEAD_DIM;
+  }
+  return 0;
+}
+
+void contiguous_strides(int64_t* s, int64_t heads, int64_t seq, int64_t d) {
+  s[2] = d;
+  s[1] = seq * d;
+  s[0] = heads * seq * d;
+}
+
+int sdpa_contiguous(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t q_seq,
+                    uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k, const void* v,
+                    void* out, double dropout_p, uint8_t is_causal, void* stream) {
+  if (dropout_p != 0.0) return -TYR_ATTN_ERR_DROPOUT;
+  if (batch > 0x7fffffffu || n_head > 0x7fffffffu || n_kv_head > 0x7fffffffu ||
+      q_seq > 0x7fffffffu || kv_seq > 0x7fffffffu || head_dim > 0x7fffffffu)
+    return -TYR_ATTN_ERR_TOO_LARGE;
+  TyrAttnPrefillArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = q; a.k = k; a.v = v; a.o = out; a.lse = nullptr;
+  a.batch = (int)batch; a.n_head = (int)n_head; a.n_kv_head = (int)n_kv_head;
+  a.q_seq = (int)q_seq; a.kv_seq = (int)kv_seq; a.head_dim = (int)head_dim;
+  contiguous_strides(a.q_stride, a.n_head, a.q_seq, a.head_dim);
+  contiguous_strides(a.k_stride, a.n_kv_head, a.kv_seq, a.head_dim);
+  contiguous_strides(a.v_stride, a.n_kv_head, a.kv_seq, a.head_dim);
+  contiguous_strides(a.o_stride, a.n_head, a.q_seq, a.head_dim);
+  a.dtype = TYR_ATTN_BF16;
+  a.is_causal = is_causal ? 1 : 0;
+  return tyr_b200_attn_prefill(&a, stream);
+}
+
+}  // namespace
+
+DeviceState* device_state(int device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState& s = g_state[device];
+  if (!s.ready) {
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess) return nullptr;
+    if (cudaSetDevice(device) != cudaSuccess) return nullptr;
+    bool ok = cudaMalloc(&s.status, sizeof(int)) == cudaSuccess &&
+              cudaMemset(s.status, 0, sizeof(int)) == cudaSuccess;
+    cudaSetDevice(prev);
+    if (!ok) return nullptr;
+    s.ready = true;
+  }
+  return &s;
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+}  // namespace tyr
+
+using namespace tyr;
+
+extern "C" {
+
+int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* a, void* stream) {
+  int rc = check_prefill(a);
+  if (rc) return rc;
+  const float scale = resolve_scale(a->scale, a->head_dim);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->check_mode) return launch_prefill_check(*a, scale, st);
+  int dev = 0;
+  if ((rc = current_device_checked(&dev))) return rc;
+  DeviceState* ds = device_state(dev);
+  if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+  return launch_prefill_sm100(*a, scale, ds->status, st);
+}
+
+int tyr_b200_sdpa_4d(uint64_t batch, uint64_t n_head, uint64_t seq, uint64_t head_dim, const void* q,
+                     const void* k, const void* v, void* out, double dropout_p, uint8_t is_causal,
+                     void* stream) {
+  return sdpa_contiguous(batch, n_head, n_head, seq, seq, head_dim, q, k, v, out, dropout_p,
+                         is_causal, stream);
+}
+
+int tyr_b200_sdpa_gqa(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                      uint64_t head_dim, const void* q, const void* k, const void* v, void* out,
+                      double dropout_p, uint8_t is_causal, uint8_t enable_gqa, void* stream) {
+  if (!enable_gqa && n_head != n_kv_head) return -TYR_ATTN_ERR_SHAPE;
+  return sdpa_contiguous(batch, n_head, n_kv_head, seq, seq, head_dim, q, k, v, out, dropout_p,
+                         is_causal, stream);
+}
+
+int tyr_b200_sdpa_gqa_qkv(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t q_seq,
+                          uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k,
+                          const void* v, void* out, double dropout_p, uint8_t is_causal,
+                          uint8_t enable_gqa, void* stream) {
+  if (!enable_gqa && n_head != n_kv_head) return -TYR_ATTN_ERR_SHAPE;
+  return sdpa_contiguous(batch, n_head, n_kv_head, q_seq, kv_seq, head_dim, q, k, v, out, dropout_p,
+                         is_causal, stream);
+}
+
+size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim,
+                                            int32_t max_kv_seq, int32_t max_splits) {
+  if (batch <= 0 || n_head <= 0 || head_dim <= 0 || max_kv_seq <= 0) return 0;
+  return decode_workspace_bytes(batch, n_head, head_dim, max_kv_seq, max_splits);
+}
+
+int tyr_b200_attn_decode(const TyrAttnDecodeArgs* a, void* stream) {
+  if (!a || !a->q || !a->o) return -TYR_ATTN_ERR_NULL;
+  const bool ragged = a->k_ptrs != nullptr || a->v_ptrs != nullptr;
+  if (ragged ? (!a->k_ptrs || !a->v_ptrs) : (!a->k || !a->v)) return -TYR_ATTN_ERR_NULL;
+  if (a->batch <= 0 || a->n_head <= 0 || a->n_kv_head <= 0 || a->max_kv_seq <= 0)
+    return -TYR_ATTN_ERR_SHAPE;
+  if (a->n_head % a->n_kv_head != 0) return -TYR_ATTN_ERR_SHAPE;
+  if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
+  if (a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
+  if ((a->k_stride[2] & 7) || (a->v_stride[2] & 7) || a->k_stride[2] <= 0 || a->v_stride[2] <= 0)
+    return -TYR_ATTN_ERR_ALIGN;
+  if (!ragged) {
+    if (!aligned16(a->k) || !aligned16(a->v)) return -TYR_ATTN_ERR_ALIGN;
+    if ((a->k_stride[0] & 7) || (a->k_stride[1] & 7) || (a->v_stride[0] & 7) || (a->v_stride[1] & 7))
+      return -TYR_ATTN_ERR_ALIGN;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->q) & 3u) || (a->q_stride[0] & 1) || (a->q_stride[1] & 1))
+    return -TYR_ATTN_ERR_ALIGN;
+  const float scale = resolve_scale(a->scale, a->head_dim);
+  return launch_decode(*a, scale, static_cast<cudaStream_t>(stream));
+}
+
+int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                        float* o_out, float* lse_out, int64_t rows, int32_t head_dim, void* stream) {
+  if (!o_a || !lse_a || !o_b || !lse_b || !o_out || !lse_out) return -TYR_ATTN_ERR_NULL;
+  if (rows <= 0 || head_dim <= 0) return -TYR_ATTN_ERR_SHAPE;
+  return launch_merge2(o_a, lse_a, o_b, lse_b, o_out, lse_out, rows, head_dim,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
+  int rc = check_prefill(a);
+  if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment
+  if (device < 0 || device >= kMaxDevices) return -TYR_ATTN_ERR_NO_DEVICE;
+  const size_t es = a->dtype == TYR_ATTN_F32 ? 4 : 2;
+  const size_t nq = (size_t)a->batch * a->n_head * a->q_seq * a->head_dim;
+  const size_t nk = (size_t)a->batch * a->n_kv_head * a->kv_seq * a->head_dim;
+  const size_t nl = (size_t)a->batch * a->n_head * a->q_seq;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  const size_t off_k = up(nq * es), off_v = off_k + up(nk * es), off_o = off_v + up(nk * es),
+               off_l = off_o + up(nq * es), total = off_l + up(nl * 4);
+
+  cudaError_t e;
+  int prev = 0;
+  if ((e = cudaGetDevice(&prev)) != cudaSuccess) return (int)e;
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return (int)e;
+  std::lock_guard<std::mutex> lock(g_host_mu);  // one host-buffer call per process at a time
+  HostStage& hs = g_stage[device];
+  auto fail = [&](int code) { cudaSetDevice(prev); return code; };
+  if (!hs.stream && (e = cudaStreamCreateWithFlags(&hs.stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail((int)e);
+  if (hs.bytes < total) {
+    if (hs.buf) cudaFree(hs.buf);
+    hs.buf = nullptr;
+    hs.bytes = 0;
+    if ((e = cudaMalloc(&hs.buf, total)) != cudaSuccess) return fail((int)e);
+    hs.bytes = total;
+  }
+  char* base = static_cast<char*>(hs.buf);
+  TyrAttnPrefillArgs d = *a;
+  d.q = base; d.k = base + off_k; d.v = base + off_v; d.o = base + off_o;
+  d.lse = a->lse ? reinterpret_cast<float*>(base + off_l) : nullptr;
+  contiguous_strides(d.q_stride, a->n_head, a->q_seq, a->head_dim);
+  contiguous_strides(d.k_stride, a->n_kv_head, a->kv_seq, a->head_dim);
+  contiguous_strides(d.v_stride, a->n_kv_head, a->kv_seq, a->head_dim);
+  contiguous_strides(d.o_stride, a->n_head, a->q_seq, a->head_dim);
+  cudaStream_t st = hs.stream;
+  if ((e = cudaMemcpyAsync(base, a->q, nq * es, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+      (e = cudaMemcpyAsync(base + off_k, a->k, nk * es, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+      (e = cudaMemcpyAsync(base + off_v, a->v, nk * es, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+    return fail((int)e);
+  rc = tyr_b200_attn_prefill(&d, st);
+  if (rc) return fail(rc);
+  if ((e = cudaMemcpyAsync(a->o, base + off_o, nq * es, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+    return fail((int)e);
+  if (a->lse &&
+      (e = cudaMemcpyAsync(a->lse, base + off_l, nl * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+    return fail((int)e);
+  e = cudaStreamSynchronize(st);
+  return fail((int)e);
+}
+
+int tyr_b200_attn_device_status(int32_t device, int32_t clear) {
+  DeviceState* ds = device_state(device);
+  if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+  int prev = 0, v = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&v, ds->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && clear) e = cudaMemset(ds->status, 0, sizeof(int));
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) return -(1000 + (int)e);
+  return v;
+}
+
+const char* tyr_b200_attn_strerror(int code) {
+  if (code == 0) return "ok";
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  switch (-code) {
+    case TYR_ATTN_ERR_NULL: return "tyr_b200_attn: a required pointer is NULL";
+    case TYR_ATTN_ERR_SHAPE: return "tyr_b200_attn: bad shape (sizes must be positive, n_head % n_kv_head == 0)";
+    case TYR_ATTN_ERR_HEAD_DIM: return "tyr_b200_attn: head_dim must be 64 or 128 (<= 256 in check mode)";
+    case TYR_ATTN_ERR_ALIGN: return "tyr_b200_attn: pointers need 16-byte alignment and strides multiples of 8 elements";
+    case TYR_ATTN_ERR_DTYPE: return "tyr_b200_attn: dtype must be bf16 (fp32 only in check mode)";
+    case TYR_ATTN_ERR_DROPOUT: return "tyr_b200_attn: dropout_p must be 0";
+    case TYR_ATTN_ERR_WORKSPACE: return "tyr_b200_attn: decode workspace missing or too small";
+    case TYR_ATTN_ERR_NO_DEVICE: return "tyr_b200_attn: no usable CUDA device or driver entry point";
+    case TYR_ATTN_ERR_DEVICE_WAIT: return "tyr_b200_attn: a bounded in-kernel wait gave up";
+    case TYR_ATTN_ERR_TOO_LARGE: return "tyr_b200_attn: size beyond the supported maximum";
+    default: return "tyr_b200_attn: unknown error";
+  }
+}
+
+int tyr_b200_attn_abi_version(void) { return TYR_ATTN_ABI_VERSION; }
+
+uint64_t tyr_b200_attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,29 @@
+// Internal launch interface shared by the .cu files of the attention library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tyr_b200_attn.h"
+
+namespace tyr {
+
+// Per-device state owned by api.cu.
+struct DeviceState {
+  int* status = nullptr;  // device word the kernels' bounded waits OR into
+  bool ready = false;
+};
+DeviceState* device_state(int device);  // lazily created; nullptr on failure
+void count_launch(int n = 1);
+
+// prefill_sm100.cu — tcgen05/TMA kernel, bf16, head_dim in {64,128}.
+int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st);
+// check_fp32.cu — fp32-FMA kernel, bf16 or fp32 I/O, any head_dim <= 256.
+int launch_prefill_check(const TyrAttnPrefillArgs& a, float scale, cudaStream_t st);
+// decode_splitkv.cu
+size_t decode_workspace_bytes(int batch, int n_head, int head_dim, int max_kv_seq, int max_splits);
+int decode_num_splits(int max_kv_seq, int max_splits, int* chunk_len);
+int launch_decode(const TyrAttnDecodeArgs& a, float scale, cudaStream_t st);
+int launch_merge2(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                  float* o_out, float* lse_out, int64_t rows, int head_dim, cudaStream_t st);
+
+}  // namespace tyr

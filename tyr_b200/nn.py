@@ -1,0 +1,264 @@
+"""Tyr's typed attention calls, served by the sm_100a kernels.
+
+Names and defaults follow the Lean declarations:
+  scaled_dot_product_attention        Tyr/Torch.lean:663-671   (is_causal := true)
+  scaledDotProductAttentionGQA        Tyr/Torch.lean:1058-1067 (enable_gqa := false)
+  scaledDotProductAttentionGQAQKV     Tyr/Torch.lean:1069-1082
+Each is a pure function returning a new tensor, like the `T #[b,h,s,d]` result of
+the Lean call.  `attentionFwd` is the launcher-style form (caller may pass the
+outputs, LSE returned) and `flashDecode` the ragged single-token decode.
+
+Tensors are torch CUDA tensors; only their data pointers, sizes and strides cross
+the C ABI, and the launch goes on torch's current stream, which is what
+`torch.cuda_current_stream` returns to Tyr (cc/src/tyr.cpp:4314-4331).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import AttnError, DecodeArgs, PrefillArgs, check
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    # the launcher checks of Tyr/GPU/Codegen/Attribute.lean:333-336, as exceptions
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("tensor must be on a CUDA device")
+        if t.dim() > 4:
+            raise ValueError("tensor rank must be <= 4")
+        if t.stride(-1) != 1:
+            raise ValueError("tensor must have unit stride on the head dimension")
+
+
+def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode) -> PrefillArgs:
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if v.shape != k.shape or Bk != B or Dk != D or o.shape != q.shape:
+        raise ValueError(f"shape mismatch: q {tuple(q.shape)} k {tuple(k.shape)} v {tuple(v.shape)}")
+    if q.dtype != k.dtype or q.dtype != v.dtype or q.dtype != o.dtype:
+        raise ValueError("q, k, v and out must share one dtype")
+    if q.dtype == torch.bfloat16:
+        dtype = _lib.TYR_ATTN_BF16
+    elif q.dtype == torch.float32:
+        dtype = _lib.TYR_ATTN_F32
+    else:
+        raise ValueError("dtype must be bfloat16 (float32 in check mode)")
+    a = PrefillArgs()
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = B, Hq, Hkv, Sq, Skv, D
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", o)):
+        getattr(a, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
+    a.dtype, a.is_causal, a.scale, a.check_mode = dtype, int(bool(is_causal)), float(scale or 0.0), int(bool(check_mode))
+    return a
+
+
+def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
+                 scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                 lse: Optional[torch.Tensor] = None, return_lse: bool = True,
+                 check_mode: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """O = softmax(Q K^T * scale + causal) V and the per-row LSE.
+
+    q [B,Hq,Sq,D]; k, v [B,Hkv,Skv,D] (Hq % Hkv == 0, query head h reads KV head
+    h // (Hq/Hkv) as repeat_interleave does, cc/src/tyr.cpp:3931-3938).  Strided
+    views are accepted (unit inner stride), e.g. the KV-cache slice of
+    Tyr/Model/Qwen/Attention.lean:195-196.  `check_mode` runs the fp32-FMA kernel.
+    Launcher convention of Examples/GPU/RunFlashAttn.lean:68-81: outputs may be
+    pre-allocated by the caller and are written in place.
+    """
+    _require_cuda(q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be [batch, heads, seq, head_dim]")
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if lse is None and return_lse:
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous()
+                            or tuple(lse.shape) != tuple(q.shape[:3])):
+        raise ValueError("lse must be a contiguous float32 [batch, n_head, q_seq] tensor")
+    a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode)
+    with torch.cuda.device(q.device):
+        check(_lib.load().tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
+    return out, lse
+
+
+def _sdpa(q, k, v, dropout_p, is_causal, enable_gqa):
+    if dropout_p != 0.0:
+        # the C ABI refuses dropout; a Tyr build keeps its LibTorch call for that case
+        raise AttnError(-6)
+    if not enable_gqa and q.shape[1] != k.shape[1]:
+        raise AttnError(-2)
+    out, _ = attentionFwd(q, k, v, is_causal=is_causal, return_lse=False)
+    return out
+
+
+def scaled_dot_product_attention(query, key, value, dropout_p: float = 0.0, is_causal: bool = True):
+    """Tyr/Torch.lean:663-671 -> lean_torch_sdpa_4d (cc/src/tyr.cpp:2563-2589)."""
+    return _sdpa(query, key, value, dropout_p, is_causal, False)
+
+
+def scaledDotProductAttentionGQA(query, key, value, dropout_p: float = 0.0, is_causal: bool = True,
+                                 enable_gqa: bool = False):
+    """Tyr/Torch.lean:1058-1067 -> lean_torch_sdpa_gqa (cc/src/tyr.cpp:3913-3949)."""
+    if query.shape[2] != key.shape[2]:
+        raise ValueError("scaledDotProductAttentionGQA needs q_seq == kv_seq; use ...GQAQKV")
+    return _sdpa(query, key, value, dropout_p, is_causal, enable_gqa)
+
+
+def scaledDotProductAttentionGQAQKV(query, key, value, dropout_p: float = 0.0, is_causal: bool = True,
+                                    enable_gqa: bool = False):
+    """Tyr/Torch.lean:1069-1082 -> lean_torch_sdpa_gqa_qkv (cc/src/tyr.cpp:4100-4133)."""
+    return _sdpa(query, key, value, dropout_p, is_causal, enable_gqa)
+
+
+def sdpa_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
+              out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+              device: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Host-buffer call: q/k/v/out are CPU tensors (pinned for full copy speed)."""
+    for t in (q, k, v):
+        if t.is_cuda or not t.is_contiguous():
+            raise ValueError("sdpa_host takes contiguous CPU tensors")
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    a = _fill_prefill(q, k, v, out, lse, is_causal, None, False)
+    check(_lib.load().tyr_b200_attn_prefill_host(ctypes.byref(a), device))
+    return out, lse
+
+
+class DecodePlan:
+    """Device-side description of a ragged KV cache for `flashDecode`.
+
+    Holds the pointer and length arrays and the split-KV workspace so that the
+    per-token call allocates nothing.  `k_list[b]`, `v_list[b]` are
+    [n_kv_head, len_b, head_dim] bf16 tensors (contiguous or with a head stride).
+    """
+
+    def __init__(self, k_list: Sequence[torch.Tensor], v_list: Sequence[torch.Tensor],
+                 n_head: int, max_splits: int = 64):
+        if len(k_list) == 0 or len(k_list) != len(v_list):
+            raise ValueError("need one K and one V tensor per sequence")
+        dev = k_list[0].device
+        self.device, self.batch, self.n_head = dev, len(k_list), n_head
+        self.n_kv_head, _, self.head_dim = k_list[0].shape
+        lens, kp, vp, hs = [], [], [], []
+        for kt, vt in zip(k_list, v_list):
+            _require_cuda(kt, vt)
+            if kt.shape != vt.shape or kt.dtype != torch.bfloat16 or kt.stride() != vt.stride():
+                raise ValueError("K and V of a sequence must match in shape, stride and be bf16")
+            if kt.stride(1) != self.head_dim:
+                raise ValueError("keys of one head must be contiguous rows")
+            lens.append(kt.shape[1]); kp.append(kt.data_ptr()); vp.append(vt.data_ptr()); hs.append(kt.stride(0))
+        self._keep = (list(k_list), list(v_list))
+        self.max_kv_seq = max(lens)
+        self.lens_host = lens
+        self.kv_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+        self.k_ptrs = torch.tensor(kp, dtype=torch.int64, device=dev)
+        self.v_ptrs = torch.tensor(vp, dtype=torch.int64, device=dev)
+        self.head_strides = torch.tensor(hs, dtype=torch.int64, device=dev)
+        self.max_splits = max_splits
+        nbytes = _lib.load().tyr_b200_attn_decode_workspace_bytes(self.batch, n_head, self.head_dim,
+                                                                  self.max_kv_seq, max_splits)
+        self.workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+        self.workspace_bytes = nbytes
+
+
+def flashDecode(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] = None,
+                out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                return_lse: bool = True):
+    """One query token per sequence over the ragged cache of `plan`.
+
+    q [B, n_head, head_dim] (or [B, n_head, 1, head_dim]) bf16.  Same result as
+    scaledDotProductAttentionGQAQKV(q[b:b+1], K_b, V_b, 0.0, false, true) for each b,
+    the call QwenAttention.forwardStep makes (Tyr/Model/Qwen/Attention.lean:198-200).
+    """
+    squeeze = q.dim() == 4
+    q3 = q[:, :, 0, :] if squeeze else q
+    _require_cuda(q3)
+    if q3.dtype != torch.bfloat16 or q3.shape != (plan.batch, plan.n_head, plan.head_dim):
+        raise ValueError("q must be bf16 [batch, n_head, head_dim]")
+    if out is None:
+        out = torch.empty((plan.batch, plan.n_head, plan.head_dim), dtype=q.dtype, device=q.device)
+    if lse is None and return_lse:
+        lse = torch.empty((plan.batch, plan.n_head), dtype=torch.float32, device=q.device)
+    a = DecodeArgs()
+    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), (lse.data_ptr() if lse is not None else None)
+    a.k = a.v = None
+    a.k_ptrs, a.v_ptrs = plan.k_ptrs.data_ptr(), plan.v_ptrs.data_ptr()
+    a.kv_lens, a.kv_head_strides = plan.kv_lens.data_ptr(), plan.head_strides.data_ptr()
+    a.batch, a.n_head, a.n_kv_head = plan.batch, plan.n_head, plan.n_kv_head
+    a.max_kv_seq, a.head_dim = plan.max_kv_seq, plan.head_dim
+    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
+    a.o_stride[:] = [out.stride(0), out.stride(1)]
+    a.k_stride[:] = [0, 0, plan.head_dim]
+    a.v_stride[:] = [0, 0, plan.head_dim]
+    a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    a.workspace, a.workspace_bytes = plan.workspace.data_ptr(), plan.workspace_bytes
+    with torch.cuda.device(q.device):
+        check(_lib.load().tyr_b200_attn_decode(ctypes.byref(a), _stream_ptr(q)))
+    if squeeze:
+        return out.unsqueeze(2), (lse.unsqueeze(2) if lse is not None else None)
+    return out, lse
+
+
+def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     kv_lens: Optional[torch.Tensor] = None, kv_len: Optional[int] = None,
+                     scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
+                     max_splits: int = 64):
+    """Decode over Tyr's dense KVCache layout [batch, n_kv_head, cap, head_dim]
+    (Tyr/Model/Qwen/Attention.lean:54-68).  `kv_len` plays the cache's shared `seq`
+    counter; `kv_lens` (int32 device tensor) makes it per sequence."""
+    _require_cuda(q, k_cache, v_cache)
+    B, Hq, D = q.shape[0], q.shape[1], q.shape[-1]
+    q3 = q[:, :, 0, :] if q.dim() == 4 else q
+    max_len = int(kv_len if kv_len is not None else k_cache.shape[2])
+    out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+    L = _lib.load()
+    nbytes = L.tyr_b200_attn_decode_workspace_bytes(B, Hq, D, max_len, max_splits)
+    if workspace is None:
+        workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    a = DecodeArgs()
+    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.k, a.v = k_cache.data_ptr(), v_cache.data_ptr()
+    a.k_ptrs = a.v_ptrs = a.kv_head_strides = None
+    a.kv_lens = kv_lens.data_ptr() if kv_lens is not None else None
+    a.batch, a.n_head, a.n_kv_head, a.max_kv_seq, a.head_dim = B, Hq, k_cache.shape[1], max_len, D
+    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
+    a.o_stride[:] = [out.stride(0), out.stride(1)]
+    a.k_stride[:] = [k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)]
+    a.v_stride[:] = [v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)]
+    a.scale, a.max_splits = float(scale or 0.0), max_splits
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    with torch.cuda.device(q.device):
+        check(L.tyr_b200_attn_decode(ctypes.byref(a), _stream_ptr(q)))
+    return out, lse
+
+
+def mergePartials(o_a, lse_a, o_b, lse_b):
+    """LSE merge of two partial results (Tyr/GPU/Kernels/RingAttn.lean:164-180)."""
+    _require_cuda(o_a, o_b, lse_a, lse_b)
+    o_a, o_b = o_a.contiguous().float(), o_b.contiguous().float()
+    lse_a, lse_b = lse_a.contiguous().float(), lse_b.contiguous().float()
+    out, lse = torch.empty_like(o_a), torch.empty_like(lse_a)
+    with torch.cuda.device(o_a.device):
+        check(_lib.load().tyr_b200_attn_merge(o_a.data_ptr(), lse_a.data_ptr(), o_b.data_ptr(),
+                                              lse_b.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                              lse_a.numel(), o_a.shape[-1], _stream_ptr(o_a)))
+    return out, lse
+
+
+def device_status(device: int = 0, clear: bool = True) -> int:
+    """Status word written by the kernels' bounded waits (0 = none gave up)."""
+    return int(_lib.load().tyr_b200_attn_device_status(device, int(clear)))
+
+
+def launch_count() -> int:
+    return int(_lib.load().tyr_b200_attn_launch_count())
