@@ -1,0 +1,78 @@
+"""The C-ABI library loads and exports what include/tyr_b200_attn.h declares (no GPU, no compute)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tyr_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "tyr_b200_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tyr_b200_\w+)\s*\(", text)))
+
+
+def test_header_and_binding_list_the_same_symbols():
+    assert declared_functions() == sorted(_lib.EXPORTS)
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    for name in declared_functions():
+        assert hasattr(built_lib, name), name
+
+
+def test_abi_version_and_error_strings(built_lib):
+    assert built_lib.tyr_b200_attn_abi_version() == 1
+    assert built_lib.tyr_b200_attn_strerror(0) == b"ok"
+    for code in range(1, 11):
+        assert built_lib.tyr_b200_attn_strerror(-code).startswith(b"tyr_b200_attn:")
+
+
+def test_struct_sizes_match_the_c_layout():
+    # 5 pointers, 6 int32, 12 int64, int32 int32 float int32
+    assert ctypes.sizeof(_lib.PrefillArgs) == 5 * 8 + 6 * 4 + 12 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
+
+
+def test_arguments_are_rejected_before_any_launch(built_lib):
+    a = _lib.PrefillArgs()
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -1          # NULL pointers
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    a.q = a.k = a.v = a.o = p
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = 1, 3, 2, 4, 4, 64
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -2          # 3 % 2 != 0
+    a.n_head = 4
+    a.head_dim = 96
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -3          # head_dim
+    a.head_dim = 64
+    a.dtype = _lib.TYR_ATTN_F32
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -5          # fp32 outside check mode
+    a.dtype = _lib.TYR_ATTN_BF16
+    a.q = p + 2
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -4          # alignment
+    # dropout is refused: a Tyr build keeps its LibTorch call for it
+    assert built_lib.tyr_b200_sdpa_4d(1, 1, 4, 64, p, p, p, p, 0.1, 1, None) == -6
+    assert built_lib.tyr_b200_sdpa_gqa(1, 4, 2, 4, 64, p, p, p, p, 0.0, 1, 0, None) == -2  # enable_gqa off
+    d = _lib.DecodeArgs()
+    assert built_lib.tyr_b200_attn_decode(ctypes.byref(d), None) == -1
+    assert built_lib.tyr_b200_attn_merge(None, None, None, None, None, None, 1, 64, None) == -1
+
+
+def test_decode_workspace_formula(built_lib):
+    f = built_lib.tyr_b200_attn_decode_workspace_bytes
+    assert f(64, 32, 128, 200, 64) == 0                      # one chunk: no scratch
+    assert f(64, 32, 128, 32768, 64) == 64 * 32 * 64 * 129 * 4
+    assert f(1, 8, 64, 1000, 64) == 1 * 8 * 4 * 65 * 4       # 256-key chunks -> 4 splits
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _lib.load()

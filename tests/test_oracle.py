@@ -1,0 +1,113 @@
+"""The CPU oracle against the committed ATen outputs and closed-form cases (no GPU)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import aten_path, c_oracle
+
+
+def rel(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def test_oracle_matches_golden_aten_outputs(golden):
+    assert len(golden) >= 6
+    for name, g in golden.items():
+        causal = bool(g["meta"][6])
+        o, lse = c_oracle.sdpa(g["q"], g["k"], g["v"], causal)
+        assert rel(o, g["o"]) < 1e-5, name
+        assert rel(lse, g["lse"]) < 1e-5, name
+
+
+def test_golden_still_matches_this_torch(golden):
+    # the fixtures were produced by the ATen operator; a torch upgrade that moved them would show here
+    g = golden["qwen_gqa_causal"]
+    o = aten_path.sdpa_gqa(torch.tensor(g["q"]), torch.tensor(g["k"]), torch.tensor(g["v"]), 0.0, True, True)
+    assert rel(o.numpy(), g["o"]) < 1e-5
+
+
+def test_online_form_equals_direct_form(golden):
+    for name, g in golden.items():
+        causal = bool(g["meta"][6])
+        o, lse = c_oracle.sdpa(g["q"], g["k"], g["v"], causal)
+        for block in (1, 7, 64):
+            o2, lse2 = c_oracle.sdpa(g["q"], g["k"], g["v"], causal, online_block=block)
+            assert rel(o2, o) < 2e-5, (name, block)
+            assert rel(lse2, lse) < 2e-5, (name, block)
+
+
+def test_single_key_softmax_is_identity():
+    # closed form used by the reference's seq=1 attention test
+    # (Tests/TestQwen35Model.lean:179-227): one key => weights == 1 => O == V, LSE == score
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((2, 4, 1, 32), dtype=np.float32)
+    k = rng.standard_normal((2, 2, 1, 32), dtype=np.float32)
+    v = rng.standard_normal((2, 2, 1, 32), dtype=np.float32)
+    o, lse = c_oracle.sdpa(q, k, v, False)
+    np.testing.assert_allclose(o, np.repeat(v, 2, axis=1), rtol=1e-6)
+    s = (q * np.repeat(k, 2, axis=1)).sum(-1) / np.sqrt(32.0)
+    np.testing.assert_allclose(lse, s, rtol=1e-5, atol=1e-6)
+
+
+def test_equal_keys_give_mean_of_values():
+    q = np.ones((1, 1, 3, 16), np.float32)
+    k = np.ones((1, 1, 10, 16), np.float32)
+    v = np.arange(160, dtype=np.float32).reshape(1, 1, 10, 16)
+    o, lse = c_oracle.sdpa(q, k, v, False)
+    np.testing.assert_allclose(o[0, 0, 0], v[0, 0].mean(0), rtol=1e-6)
+    np.testing.assert_allclose(lse, 4.0 + np.log(10.0), rtol=1e-6)   # 16/sqrt(16) + log n
+    o, lse = c_oracle.sdpa(q, k, v, True)                             # row i sees keys 0..i
+    np.testing.assert_allclose(o[0, 0, 2], v[0, 0, :3].mean(0), rtol=1e-6)
+    np.testing.assert_allclose(lse[0, 0], 4.0 + np.log([1.0, 2.0, 3.0]), rtol=1e-6)
+
+
+def test_gqa_equals_repeat_interleave():
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((1, 6, 20, 32), dtype=np.float32)
+    k = rng.standard_normal((1, 2, 20, 32), dtype=np.float32)
+    v = rng.standard_normal((1, 2, 20, 32), dtype=np.float32)
+    o, lse = c_oracle.sdpa(q, k, v, True)
+    o2, lse2 = c_oracle.sdpa(q, np.repeat(k, 3, axis=1), np.repeat(v, 3, axis=1), True)
+    np.testing.assert_array_equal(o, o2)
+    np.testing.assert_array_equal(lse, lse2)
+
+
+def test_merge_of_key_halves_equals_full_attention():
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((1, 2, 5, 64), dtype=np.float32)
+    k = rng.standard_normal((1, 2, 50, 64), dtype=np.float32)
+    v = rng.standard_normal((1, 2, 50, 64), dtype=np.float32)
+    o, lse = c_oracle.sdpa(q, k, v, False)
+    oa, la = c_oracle.sdpa(q, k[:, :, :20], v[:, :, :20], False)
+    ob, lb = c_oracle.sdpa(q, k[:, :, 20:], v[:, :, 20:], False)
+    om, lm = c_oracle.merge2(oa.reshape(-1, 64), la.reshape(-1), ob.reshape(-1, 64), lb.reshape(-1))
+    assert rel(om.reshape(o.shape), o) < 1e-6
+    assert rel(lm.reshape(lse.shape), lse) < 1e-6
+
+
+def test_decode_step_equals_last_row_of_causal_prefill():
+    # cached decode == uncached prefill, the parity the reference pins at model level
+    # (Tests/TestQwen3Model.lean:36-55)
+    rng = np.random.default_rng(4)
+    q = rng.standard_normal((2, 4, 33, 64), dtype=np.float32)
+    k = rng.standard_normal((2, 2, 33, 64), dtype=np.float32)
+    v = rng.standard_normal((2, 2, 33, 64), dtype=np.float32)
+    o, lse = c_oracle.sdpa(q, k, v, True)
+    o1, lse1 = c_oracle.sdpa(q[:, :, -1:], k, v, False)
+    assert rel(o1, o[:, :, -1:]) < 1e-6
+    assert rel(lse1, lse[:, :, -1:]) < 1e-6
+
+
+def test_bf16_round_matches_torch():
+    rng = np.random.default_rng(5)
+    x = np.concatenate([rng.standard_normal(4096).astype(np.float32) * 100,
+                        np.array([0.0, -0.0, 1.0, 65504.0, 1e-40, np.inf, -np.inf], np.float32)])
+    ref = torch.tensor(x).bfloat16().float().numpy()
+    np.testing.assert_array_equal(c_oracle.bf16_round(x), ref)
+
+
+def test_oracle_rejects_bad_shapes():
+    q = np.zeros((1, 3, 2, 8), np.float32)
+    k = np.zeros((1, 2, 2, 8), np.float32)
+    with pytest.raises(ValueError):
+        c_oracle.sdpa(q, k, k, False)

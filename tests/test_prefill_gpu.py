@@ -1,0 +1,253 @@
+"""Parity of the sm_100a prefill kernels with the CPU oracle, through the C ABI."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import CHECK_REL, LSE_REL, O_MAX_ABS
+from oracle import c_oracle
+from tyr_b200 import _lib, nn as tnn
+from tyr_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def oracle(q, k, v, causal):
+    """fp32 CPU result on the bf16-rounded values (Examples/GPU/RunFlashAttn.lean:30-36)."""
+    return c_oracle.sdpa(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), causal)
+
+
+def assert_parity(o, lse, ro, rlse, tag=""):
+    o = o.float().cpu().numpy()
+    assert not np.isnan(o).any(), tag
+    assert np.abs(o - ro).max() <= O_MAX_ABS, (tag, float(np.abs(o - ro).max()))
+    if lse is not None:
+        lse = lse.cpu().numpy()
+        err = np.abs(lse - rlse) / np.maximum(np.abs(rlse), 1.0)
+        assert err.max() <= LSE_REL, (tag, float(err.max()))
+
+
+def randn(*shape, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(*shape, generator=g).bfloat16()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert tnn.device_status(0, True) == 0, "a bounded in-kernel wait gave up"
+
+
+def test_golden_vectors(golden):
+    for name, g in golden.items():
+        causal = bool(g["meta"][6])
+        D = int(g["meta"][5])
+        q, k, v = (torch.tensor(g[x]).bfloat16().to(DEV) for x in ("q", "k", "v"))
+        o, lse = tnn.attentionFwd(q, k, v, is_causal=causal)
+        assert_parity(o, lse, g["o"], g["lse"], name)
+        # check mode on the same (bf16-exact) fp32 inputs
+        qf, kf, vf = (torch.tensor(g[x]).to(DEV) for x in ("q", "k", "v"))
+        o32, lse32 = tnn.attentionFwd(qf, kf, vf, is_causal=causal, check_mode=True)
+        scale = np.abs(g["o"]).max()
+        assert np.abs(o32.cpu().numpy() - g["o"]).max() / scale <= CHECK_REL, name
+        assert (np.abs(lse32.cpu().numpy() - g["lse"]) / np.maximum(np.abs(g["lse"]), 1.0)).max() <= CHECK_REL, name
+
+
+@pytest.mark.parametrize("S", [1, 63, 64, 65, 127, 128, 129, 255, 256, 257, 383, 512, 700])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_sequence_lengths(S, D, causal):
+    q, k, v = randn(2, 4, S, D, seed=S), randn(2, 2, S, D, seed=S + 1), randn(2, 2, S, D, seed=S + 2)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=causal)
+    ro, rlse = oracle(q, k, v, causal)
+    assert_parity(o, lse, ro, rlse, (S, D, causal))
+
+
+@pytest.mark.parametrize("Sq,Skv", [(1, 300), (5, 9), (100, 700), (300, 40), (129, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_query_and_key_lengths_differ(Sq, Skv, causal):
+    # lean_torch_sdpa_gqa_qkv; causal is top-left aligned as in ATen (key j masked when j > i)
+    q, k, v = randn(1, 4, Sq, 128, seed=1), randn(1, 1, Skv, 128, seed=2), randn(1, 1, Skv, 128, seed=3)
+    o = tnn.scaledDotProductAttentionGQAQKV(q.to(DEV), k.to(DEV), v.to(DEV), 0.0, causal, True)
+    ro, _ = oracle(q, k, v, causal)
+    assert_parity(o, None, ro, None, (Sq, Skv, causal))
+
+
+def test_typed_calls_mirror_the_lean_externs():
+    q, k, v = randn(2, 4, 200, 64, seed=7), randn(2, 4, 200, 64, seed=8), randn(2, 4, 200, 64, seed=9)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    o = tnn.scaled_dot_product_attention(qd, kd, vd)          # is_causal defaults to true
+    assert_parity(o, None, oracle(q, k, v, True)[0], None)
+    o = tnn.scaled_dot_product_attention(qd, kd, vd, 0.0, False)
+    assert_parity(o, None, oracle(q, k, v, False)[0], None)
+    kg, vg = k[:, :2].contiguous(), v[:, :2].contiguous()
+    o = tnn.scaledDotProductAttentionGQA(qd, kg.to(DEV), vg.to(DEV), 0.0, True, True)
+    assert_parity(o, None, oracle(q, kg, vg, True)[0], None)
+    with pytest.raises(_lib.AttnError):                        # enable_gqa = false with fewer KV heads
+        tnn.scaledDotProductAttentionGQA(qd, kg.to(DEV), vg.to(DEV), 0.0, True, False)
+    with pytest.raises(_lib.AttnError):                        # dropout stays with LibTorch
+        tnn.scaled_dot_product_attention(qd, kd, vd, 0.1, True)
+
+
+def test_raw_c_abi_entry_points():
+    L = _lib.load()
+    q, k, v = randn(1, 4, 150, 128, seed=11), randn(1, 2, 150, 128, seed=12), randn(1, 2, 150, 128, seed=13)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out = torch.empty_like(qd)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = L.tyr_b200_sdpa_gqa(1, 4, 2, 150, 128, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(),
+                             out.data_ptr(), 0.0, 1, 1, st)
+    assert rc == 0
+    assert_parity(out, None, oracle(q, k, v, True)[0], None)
+    q1 = qd[:, :, -1:].contiguous()
+    out1 = torch.empty_like(q1)
+    rc = L.tyr_b200_sdpa_gqa_qkv(1, 4, 2, 1, 150, 128, q1.data_ptr(), kd.data_ptr(), vd.data_ptr(),
+                                 out1.data_ptr(), 0.0, 0, 1, st)
+    assert rc == 0
+    # cached decode == last row of the causal prefill (Tests/TestQwen3Model.lean:36-55)
+    assert (out1.float() - out[:, :, -1:].float()).abs().max().item() <= 1e-2
+    k4, v4 = kd.repeat_interleave(2, 1), vd.repeat_interleave(2, 1)
+    out4 = torch.empty_like(qd)
+    assert L.tyr_b200_sdpa_4d(1, 4, 150, 128, qd.data_ptr(), k4.data_ptr(), v4.data_ptr(),
+                              out4.data_ptr(), 0.0, 1, st) == 0
+    assert torch.equal(out4, out)      # GQA index map == repeat_interleave, bit for bit
+
+
+def test_strided_views_and_caller_allocated_outputs():
+    # K/V as the slice of a larger cache (Tyr/Model/Qwen/Attention.lean:195-196)
+    cap, L_ = 512, 300
+    kc, vc = randn(2, 2, cap, 128, seed=21).to(DEV), randn(2, 2, cap, 128, seed=22).to(DEV)
+    q = randn(2, 4, L_, 128, seed=23).to(DEV)
+    k, v = kc[:, :, :L_], vc[:, :, :L_]
+    assert not k.is_contiguous()
+    out = torch.zeros(2, 4, L_, 128, dtype=torch.bfloat16, device=DEV)
+    lse = torch.zeros(2, 4, L_, dtype=torch.float32, device=DEV)
+    o2, lse2 = tnn.attentionFwd(q, k, v, is_causal=True, out=out, lse=lse)
+    assert o2.data_ptr() == out.data_ptr()
+    ro, rlse = oracle(q.cpu(), k.cpu(), v.cpu(), True)
+    assert_parity(out, lse, ro, rlse)
+    # [B,S,H,D] storage viewed as [B,H,S,D]
+    qb = randn(2, 200, 4, 64, seed=24).to(DEV)
+    kb, vb = randn(2, 200, 2, 64, seed=25).to(DEV), randn(2, 200, 2, 64, seed=26).to(DEV)
+    ob = torch.empty(2, 200, 4, 64, dtype=torch.bfloat16, device=DEV)
+    tnn.attentionFwd(qb.transpose(1, 2), kb.transpose(1, 2), vb.transpose(1, 2), is_causal=True,
+                     out=ob.transpose(1, 2), return_lse=False)
+    ro, _ = oracle(qb.transpose(1, 2).cpu(), kb.transpose(1, 2).cpu(), vb.transpose(1, 2).cpu(), True)
+    assert_parity(ob.transpose(1, 2), None, ro, None)
+
+
+def test_rows_outside_the_tensor_are_not_written():
+    S = 130
+    q, k, v = randn(1, 2, S, 128, seed=31), randn(1, 2, S, 128, seed=32), randn(1, 2, S, 128, seed=33)
+    big = torch.full((1, 2, S + 64, 128), 7.0, dtype=torch.bfloat16, device=DEV)
+    tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=False, out=big[:, :, :S], return_lse=False)
+    assert (big[:, :, S:] == 7.0).all()
+
+
+def test_large_logits_and_scale_argument():
+    q, k, v = randn(1, 2, 256, 128, seed=41) * 6, randn(1, 2, 256, 128, seed=42) * 6, randn(1, 2, 256, 128, seed=43)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True)
+    ro, rlse = oracle(q, k, v, True)
+    assert_parity(o, lse, ro, rlse)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=False, scale=0.01)
+    ro, rlse = c_oracle.sdpa(q.float().numpy(), k.float().numpy(), v.float().numpy(), False, scale=0.01)
+    assert_parity(o, lse, ro, rlse)
+
+
+def test_check_mode_fp32_inputs_within_1e5():
+    g = torch.Generator(device="cpu").manual_seed(51)
+    q, k, v = (torch.randn(2, 4, 300, 96, generator=g) for _ in range(3))
+    k, v = k[:, :2].contiguous(), v[:, :2].contiguous()
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, check_mode=True)
+    ro, rlse = c_oracle.sdpa(q.numpy(), k.numpy(), v.numpy(), True)
+    assert np.abs(o.cpu().numpy() - ro).max() / np.abs(ro).max() <= CHECK_REL
+    assert (np.abs(lse.cpu().numpy() - rlse) / np.maximum(np.abs(rlse), 1.0)).max() <= CHECK_REL
+
+
+@pytest.mark.parametrize("name,batch,heads,seq", [
+    ("gpt_char", 4, (6, 6), None),               # configs[0] shape, fewer batches
+    ("qwen3_0p6b_prefill", 1, (4, 2), 2048),     # configs[1] head geometry
+    ("flux_mmdit", 1, (2, 2), 1152),             # configs[4], non-causal
+])
+def test_workload_shapes_against_oracle(name, batch, heads, seq):
+    w = W.WORKLOADS[name]
+    q, k, v = W.make_prefill(w, batch=batch, heads=heads, seq=seq)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=w.causal)
+    ro, rlse = oracle(q, k, v, w.causal)
+    assert_parity(o, lse, ro, rlse, name)
+
+
+def _sampled_rows_vs_oracle(q, k, v, o, lse, causal, n=48, seed=0):
+    """Exact oracle answer for a sample of (b, h, row): the row only needs its own keys."""
+    B, Hq, S, D = q.shape
+    g = Hq // k.shape[1]
+    rng = np.random.default_rng(seed)
+    for _ in range(n):
+        b, h, i = int(rng.integers(B)), int(rng.integers(Hq)), int(rng.integers(S))
+        if _ % 8 == 0:
+            i = [0, S - 1, 127, 128, 255, 256, S // 2][(_ // 8) % 7]
+        n_keys = i + 1 if causal else k.shape[2]
+        qr = q[b, h, i].float().cpu().numpy().reshape(1, 1, 1, D)
+        kr = k[b, h // g, :n_keys].float().cpu().numpy().reshape(1, 1, n_keys, D)
+        vr = v[b, h // g, :n_keys].float().cpu().numpy().reshape(1, 1, n_keys, D)
+        ro, rl = c_oracle.sdpa(qr, kr, vr, False)
+        assert np.abs(o[b, h, i].float().cpu().numpy() - ro[0, 0, 0]).max() <= O_MAX_ABS, (b, h, i)
+        assert abs(lse[b, h, i].item() - rl[0, 0, 0]) / max(abs(rl[0, 0, 0]), 1.0) <= LSE_REL, (b, h, i)
+
+
+@pytest.mark.parametrize("name", ["qwen3_0p6b_prefill", "qwen3_8b_prefill", "flux_mmdit", "gpt_char"])
+def test_full_size_workloads_by_sampled_rows_and_properties(name):
+    w = W.WORKLOADS[name]
+    q, k, v = (t.to(DEV) for t in W.make_prefill(w))
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=w.causal)
+    assert not torch.isnan(o.float()).any()
+    _sampled_rows_vs_oracle(q, k, v, o, lse, w.causal)
+    # property 1: the output is a convex combination of V rows
+    vmax = v.float().abs().amax(dim=(2,), keepdim=True).repeat_interleave(w.n_head // w.n_kv_head, 1)
+    assert (o.float().abs() <= vmax * 1.01 + 1e-3).all()
+    # property 2: linear in V (same softmax weights): attn(2V) == 2 attn(V) up to bf16 rounding
+    o2, lse2 = tnn.attentionFwd(q, k, v * 2, is_causal=w.causal)
+    assert torch.equal(lse2, lse)
+    assert (o2.float() - 2 * o.float()).abs().max().item() <= 2e-2
+    # property 3: the tensor-core kernel agrees with the fp32-FMA kernel on one (batch, KV head)
+    b, hk, g = w.batch - 1, w.n_kv_head - 1, w.n_head // w.n_kv_head
+    qs = q[b:b + 1, hk * g:(hk + 1) * g]
+    oc, lc = tnn.attentionFwd(qs, k[b:b + 1, hk:hk + 1], v[b:b + 1, hk:hk + 1], is_causal=w.causal,
+                              check_mode=True)
+    assert (oc.float() - o[b:b + 1, hk * g:(hk + 1) * g].float()).abs().max().item() <= O_MAX_ABS
+    assert ((lc - lse[b:b + 1, hk * g:(hk + 1) * g]).abs() / lc.abs().clamp(min=1)).max().item() <= LSE_REL
+
+
+def test_merge_entry_point_against_oracle_and_full_attention():
+    q, k, v = randn(1, 2, 64, 128, seed=61), randn(1, 2, 600, 128, seed=62), randn(1, 2, 600, 128, seed=63)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    oa, la = tnn.attentionFwd(qd, kd[:, :, :256], vd[:, :, :256], is_causal=False)
+    ob, lb = tnn.attentionFwd(qd, kd[:, :, 256:], vd[:, :, 256:], is_causal=False)
+    om, lm = tnn.mergePartials(oa.float().reshape(-1, 128), la.reshape(-1), ob.float().reshape(-1, 128),
+                               lb.reshape(-1))
+    ro, rl = c_oracle.merge2(oa.float().cpu().numpy().reshape(-1, 128), la.cpu().numpy().reshape(-1),
+                             ob.float().cpu().numpy().reshape(-1, 128), lb.cpu().numpy().reshape(-1))
+    assert np.abs(om.cpu().numpy() - ro).max() <= 1e-5
+    assert np.abs(lm.cpu().numpy() - rl).max() <= 1e-5
+    fo, fl = oracle(q, k, v, False)
+    assert np.abs(om.cpu().numpy().reshape(fo.shape) - fo).max() <= O_MAX_ABS
+    assert np.abs(lm.cpu().numpy().reshape(fl.shape) - fl).max() <= 1e-3 * np.abs(fl).max()
+
+
+def test_host_buffer_call():
+    q, k, v = randn(2, 4, 300, 128, seed=71), randn(2, 2, 300, 128, seed=72), randn(2, 2, 300, 128, seed=73)
+    qp, kp, vp = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    lse = torch.empty(2, 4, 300, dtype=torch.float32).pin_memory()
+    o, lse = tnn.sdpa_host(qp, kp, vp, is_causal=True, lse=lse)
+    assert not o.is_cuda
+    ro, rlse = oracle(q, k, v, True)
+    assert_parity(o, lse, ro, rlse)
+
+
+def test_launches_are_counted():
+    n0 = tnn.launch_count()
+    q = randn(1, 1, 64, 64).to(DEV)
+    tnn.attentionFwd(q, q, q)
+    assert tnn.launch_count() == n0 + 1
