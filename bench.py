@@ -33,8 +33,8 @@ METRIC = "attention_tflops_causal_adjusted"
 UNIT = "TFLOP/s"
 DEFAULT_WORKLOAD = "qwen3_0p6b_prefill"
 # dram__bytes_read.sum + dram__bytes_write.sum of one prefill launch, from the ncu
-# capture summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": None}
+# capture summarised in profiles/prefill_kernel_qwen3_0p6b_prefill.md (None: no capture for that workload)
+NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": 177458944}
 
 
 def load_peaks():

@@ -1,0 +1,172 @@
+// Lean-facing shim over the C ABI of include/tyr_b200_attn.h.
+//
+// This file is meant to be dropped into Tyr's cc/src/ next to tyr.cpp and linked
+// into libTyrC (cc/Makefile picks up cc/src/*.cpp).  It lifts raw device pointers,
+// sizes and strides out of Tyr's tensor handles (Lean external objects owning a
+// c10::TensorImpl*, cc/src/tyr.cpp:111-159) and calls the library; no ATen
+// operator runs between pointer extraction and launch, only the allocation of the
+// result tensor for the pure (surface A) entry points.
+//
+// It compiles only where <lean/lean.h> and the LibTorch headers exist (same
+// __has_include idiom as cc/src/tyr.cpp:72-81); elsewhere it is an empty
+// translation unit.  The image this library is developed in has no Lean toolchain.
+#if defined(__has_include)
+#if __has_include(<lean/lean.h>) && __has_include(<torch/torch.h>)
+#define TYR_B200_SHIM_ENABLED 1
+#endif
+#endif
+
+#ifdef TYR_B200_SHIM_ENABLED
+#include <lean/lean.h>
+#include <torch/torch.h>
+#if __has_include(<c10/cuda/CUDAStream.h>)
+#include <c10/cuda/CUDAStream.h>
+#define TYR_B200_HAS_CUDA_STREAM 1
+#endif
+
+#include <cstring>
+
+#include "tyr_b200_attn.h"
+
+// provided by cc/src/tyr.cpp
+torch::Tensor borrowTensor(b_lean_obj_arg o);
+lean_object* giveTensor(torch::Tensor t);
+
+namespace {
+
+lean_object* io_error(const char* msg) {
+  return lean_io_result_mk_error(lean_mk_io_user_error(lean_mk_string(msg)));
+}
+
+bool eligible(const torch::Tensor& t) {
+  return t.defined() && t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 4 &&
+         t.stride(3) == 1;
+}
+
+void fill_strides(int64_t* s, const torch::Tensor& t) {
+  s[0] = t.stride(0);
+  s[1] = t.stride(1);
+  s[2] = t.stride(2);
+}
+
+// Fills `a` from [B,H,S,D] tensors.  `o` must already exist.
+void fill_args(TyrAttnPrefillArgs& a, const torch::Tensor& q, const torch::Tensor& k,
+               const torch::Tensor& v, const torch::Tensor& o, float* lse, bool is_causal) {
+  std::memset(&a, 0, sizeof(a));
+  a.q = q.data_ptr();
+  a.k = k.data_ptr();
+  a.v = v.data_ptr();
+  a.o = o.data_ptr();
+  a.lse = lse;
+  a.batch = (int32_t)q.size(0);
+  a.n_head = (int32_t)q.size(1);
+  a.q_seq = (int32_t)q.size(2);
+  a.head_dim = (int32_t)q.size(3);
+  a.n_kv_head = (int32_t)k.size(1);
+  a.kv_seq = (int32_t)k.size(2);
+  fill_strides(a.q_stride, q);
+  fill_strides(a.k_stride, k);
+  fill_strides(a.v_stride, v);
+  fill_strides(a.o_stride, o);
+  a.dtype = TYR_ATTN_BF16;
+  a.is_causal = is_causal ? 1 : 0;
+}
+
+void* current_stream(const torch::Tensor& t) {
+#ifdef TYR_B200_HAS_CUDA_STREAM
+  return c10::cuda::getCurrentCUDAStream(t.get_device()).stream();
+#else
+  (void)t;
+  return nullptr;
+#endif
+}
+
+}  // namespace
+
+// Surface A helper: try the B200 kernel; false means "not eligible, keep the LibTorch
+// call".  The pure Lean externs cannot fail, so every rejection falls through.
+//   usage inside lean_torch_sdpa_gqa (cc/src/tyr.cpp:3913-3949), before the
+//   repeat_interleave:   torch::Tensor out; if (tyr_b200_try_sdpa(q, k, v, dropout_p,
+//   is_causal, enable_gqa, &out)) return giveTensor(out);
+bool tyr_b200_try_sdpa(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
+                       double dropout_p, bool is_causal, bool enable_gqa, torch::Tensor* out) {
+  if (dropout_p != 0.0 || !eligible(q) || !eligible(k) || !eligible(v)) return false;
+  if (!enable_gqa && q.size(1) != k.size(1)) return false;
+  if (k.size(1) == 0 || q.size(1) % k.size(1) != 0) return false;
+  if (q.size(3) != 64 && q.size(3) != 128) return false;
+  torch::Tensor o = torch::empty(q.sizes(), q.options());  // allocation only
+  TyrAttnPrefillArgs a;
+  fill_args(a, q, k, v, o, nullptr, is_causal);
+  if (tyr_b200_attn_prefill(&a, current_stream(q)) != 0) return false;
+  *out = o;
+  return true;
+}
+
+// Surface B: launcher in the shape of the generated lean_launch_* functions
+// (Tyr/GPU/Codegen/Attribute.lean:346-386): borrowed tensor handles, scalars,
+// stream last, IO result.  Outputs are caller-allocated and written in place.
+extern "C" lean_object* lean_launch_tyrB200AttnFwd(b_lean_obj_arg q_, b_lean_obj_arg k_,
+                                                   b_lean_obj_arg v_, b_lean_obj_arg o_,
+                                                   b_lean_obj_arg lse_, uint8_t is_causal,
+                                                   uint64_t stream, lean_object* /*w*/) {
+  try {
+    auto q = borrowTensor(q_), k = borrowTensor(k_), v = borrowTensor(v_), o = borrowTensor(o_),
+         lse = borrowTensor(lse_);
+    for (const auto* t : {&q, &k, &v, &o}) {
+      if (!t->is_cuda()) return io_error("tyrB200AttnFwd: tensors must be CUDA tensors");
+      if (t->dim() != 4) return io_error("tyrB200AttnFwd: tensors must be [batch, heads, seq, head_dim]");
+      if (t->scalar_type() != at::kBFloat16) return io_error("tyrB200AttnFwd: tensors must be bfloat16");
+      if (t->stride(3) != 1) return io_error("tyrB200AttnFwd: head_dim must have unit stride");
+    }
+    if (!lse.is_cuda() || !lse.is_contiguous() || lse.scalar_type() != at::kFloat ||
+        lse.numel() != q.size(0) * q.size(1) * q.size(2))
+      return io_error("tyrB200AttnFwd: lse must be a contiguous float32 [batch, n_head, seq] CUDA tensor");
+    TyrAttnPrefillArgs a;
+    fill_args(a, q, k, v, o, lse.data_ptr<float>(), is_causal != 0);
+    int rc = tyr_b200_attn_prefill(&a, reinterpret_cast<void*>(stream));
+    if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
+    return lean_io_result_mk_ok(lean_box(0));
+  } catch (const std::exception& e) {
+    return io_error(e.what());
+  }
+}
+
+// Decode over Tyr's dense KVCache ([batch, n_kv_head, maxLen, head_dim],
+// Tyr/Model/Qwen/Attention.lean:54-68) with the cache's shared `seq` counter as kv_len.
+extern "C" lean_object* lean_launch_tyrB200AttnDecode(b_lean_obj_arg q_, b_lean_obj_arg kcache_,
+                                                      b_lean_obj_arg vcache_, b_lean_obj_arg o_,
+                                                      b_lean_obj_arg workspace_, uint64_t kv_len,
+                                                      uint64_t stream, lean_object* /*w*/) {
+  try {
+    auto q = borrowTensor(q_), kc = borrowTensor(kcache_), vc = borrowTensor(vcache_),
+         o = borrowTensor(o_), ws = borrowTensor(workspace_);
+    if (!q.is_cuda() || !kc.is_cuda() || !vc.is_cuda() || !o.is_cuda() || !ws.is_cuda())
+      return io_error("tyrB200AttnDecode: tensors must be CUDA tensors");
+    if (q.dim() != 4 || q.size(2) != 1 || kc.dim() != 4 || vc.dim() != 4 || o.dim() != 4)
+      return io_error("tyrB200AttnDecode: q/o must be [batch, n_head, 1, head_dim], caches 4-D");
+    if (kv_len == 0 || (int64_t)kv_len > kc.size(2)) return io_error("tyrB200AttnDecode: bad kv_len");
+    TyrAttnDecodeArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.q = q.data_ptr();
+    a.o = o.data_ptr();
+    a.k = kc.data_ptr();
+    a.v = vc.data_ptr();
+    a.batch = (int32_t)q.size(0);
+    a.n_head = (int32_t)q.size(1);
+    a.n_kv_head = (int32_t)kc.size(1);
+    a.max_kv_seq = (int32_t)kv_len;
+    a.head_dim = (int32_t)q.size(3);
+    a.q_stride[0] = q.stride(0); a.q_stride[1] = q.stride(1);
+    a.o_stride[0] = o.stride(0); a.o_stride[1] = o.stride(1);
+    fill_strides(a.k_stride, kc);
+    fill_strides(a.v_stride, vc);
+    a.workspace = ws.data_ptr();
+    a.workspace_bytes = (size_t)ws.nbytes();
+    int rc = tyr_b200_attn_decode(&a, reinterpret_cast<void*>(stream));
+    if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
+    return lean_io_result_mk_ok(lean_box(0));
+  } catch (const std::exception& e) {
+    return io_error(e.what());
+  }
+}
+#endif  // TYR_B200_SHIM_ENABLED

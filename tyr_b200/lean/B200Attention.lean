@@ -1,0 +1,39 @@
+/-
+  Tyr/GPU/B200Attention.lean — Lean 4 bindings of the B200 attention operator.
+
+  Not compiled in the image this library is developed in (no Lean toolchain);
+  kept signature-identical to the launcher declarations Tyr generates
+  (Tyr/GPU/Codegen/Attribute.lean:390-437) and to the typed calls in
+  Tyr/Torch.lean:663-671, 1058-1082.
+-/
+import Tyr.Torch
+import Tyr.GPU.Codegen.TileTypes
+
+namespace Tyr.GPU.B200
+
+open torch
+
+/-- Launcher form: caller-allocated `out` and `lse`, explicit stream, IO error on
+    rejection (shape, dtype, alignment, dropout).  C side: `lean_launch_tyrB200AttnFwd`. -/
+@[extern "lean_launch_tyrB200AttnFwd"]
+opaque tyrB200AttnFwd.launch
+    (q k v out lse : @& Tensor) (isCausal : UInt8) (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- Single-token decode over the dense KV cache with the cache's `seq` counter as `kvLen`.
+    C side: `lean_launch_tyrB200AttnDecode`. -/
+@[extern "lean_launch_tyrB200AttnDecode"]
+opaque tyrB200AttnDecode.launch
+    (q kCache vCache out workspace : @& Tensor) (kvLen : UInt64) (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- Typed wrapper: output and per-row LSE of causal / non-causal GQA attention. -/
+def attentionFwd {b hq hkv s d : UInt64}
+    (q : T #[b, hq, s, d]) (k v : T #[b, hkv, s, d]) (isCausal : Bool := true)
+    : IO (T #[b, hq, s, d] × T #[b, hq, s]) := do
+  let out : T #[b, hq, s, d] := torch.zeros_like q
+  let lse : T #[b, hq, s] := torch.zeros #[b, hq, s] false (torch.device q)
+  let lse32 := torch.toFloat' lse
+  let stream ← torch.cuda_current_stream
+  tyrB200AttnFwd.launch q k v out lse32 (if isCausal then 1 else 0) stream
+  pure (out, lse32)
+
+end Tyr.GPU.B200
