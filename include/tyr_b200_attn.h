@@ -136,6 +136,32 @@ size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32
                                             int32_t max_kv_seq, int32_t max_splits);
 int tyr_b200_attn_decode(const TyrAttnDecodeArgs* args, void* stream);
 
+/* Decode for callers that must not allocate device memory.
+ *
+ * No counterpart in the reference; added for hosts of this library that cannot
+ * call cudaMalloc at the point where they decode: a serving loop whose memory
+ * pool already owns the whole device, a latency-critical token loop that cannot
+ * afford the device-wide synchronisation an allocation implies, or a plugin
+ * that is forbidden to touch the allocator of the process it is loaded into.
+ * It is tyr_b200_attn_decode with the
+ * split-KV scratch taken from a fixed array of
+ * TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES inside the library image instead of
+ * args->workspace (args->workspace and args->workspace_bytes are ignored).
+ * Every GPU that loads the library carries that array until the process exits.
+ *
+ *  - Sizes whose scratch need (tyr_b200_attn_decode_workspace_bytes) exceeds
+ *    the array are refused with -TYR_ATTN_ERR_TOO_LARGE; lower max_splits or
+ *    the batch, or use tyr_b200_attn_decode with your own workspace.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - The call itself runs no cudaMalloc, cudaFree or allocating library routine.
+ *  - All calls on a device share the one array and it keeps the previous
+ *    call's contents.  Nothing in it needs clearing (each call writes every
+ *    slot it later reads), but two calls that overlap on the GPU, e.g. on two
+ *    streams, race on it: order them on one stream or with events. */
+#define TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES (16u << 20)
+int tyr_b200_attn_decode_static(const TyrAttnDecodeArgs* args, void* stream);
+
 /* LSE merge of two partial attention results over disjoint key sets (the
  * reduction Tyr states in ringAttnReduce, Tyr/GPU/Kernels/RingAttn.lean:164-180):
  *   L = Lr + log(1 + exp(Lb - Lr));  O = Or*exp(Lr-L) + Ob*exp(Lb-L).

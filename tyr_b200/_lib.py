@@ -15,11 +15,13 @@ c_i32, c_i64, c_u64, c_f32, c_f64, c_u8 = (ctypes.c_int32, ctypes.c_int64, ctype
 vp = ctypes.c_void_p
 
 TYR_ATTN_BF16, TYR_ATTN_F32 = 0, 1
+DECODE_STATIC_SCRATCH_BYTES = 16 << 20   # TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES
 
 # every symbol include/tyr_b200_attn.h declares
 EXPORTS = [
     "tyr_b200_attn_prefill", "tyr_b200_sdpa_4d", "tyr_b200_sdpa_gqa", "tyr_b200_sdpa_gqa_qkv",
-    "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_merge",
+    "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_decode_static",
+    "tyr_b200_attn_merge",
     "tyr_b200_attn_prefill_host", "tyr_b200_attn_device_status", "tyr_b200_attn_strerror",
     "tyr_b200_attn_abi_version", "tyr_b200_attn_launch_count",
 ]
@@ -75,6 +77,8 @@ def load() -> ctypes.CDLL:
     L.tyr_b200_attn_decode_workspace_bytes.restype = ctypes.c_size_t
     L.tyr_b200_attn_decode.argtypes = [ctypes.POINTER(DecodeArgs), vp]
     L.tyr_b200_attn_decode.restype = ctypes.c_int
+    L.tyr_b200_attn_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), vp]
+    L.tyr_b200_attn_decode_static.restype = ctypes.c_int
     L.tyr_b200_attn_merge.argtypes = [vp] * 6 + [c_i64, c_i32, vp]
     L.tyr_b200_attn_merge.restype = ctypes.c_int
     L.tyr_b200_attn_device_status.argtypes = [c_i32, c_i32]

@@ -15,6 +15,8 @@
 // keeps its own (max, sum, O); the four warps merge through shared memory.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "attn_internal.h"
 
 namespace tyr {
@@ -423,3 +425,61 @@ int launch_merge2(const float* o_a, const float* lse_a, const float* o_b, const 
 }
 
 }  // namespace tyr
+
+// ---------------------------------------------------------------------------
+// Decode without any allocation: the split-KV scratch lives in a fixed array
+// inside the library image instead of a caller-provided workspace.
+// ---------------------------------------------------------------------------
+namespace tyr {
+namespace {
+
+constexpr size_t kStaticScratchBytes = TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES;
+
+// Held by every GPU that loads this library until the process exits.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mu;
+void* g_static_scratch_ptr[kMaxStaticDevices] = {};  // device address of the array, per device
+
+// In host code `g_decode_static_scratch` is only a stand-in for the symbol; the
+// address a kernel can use has to be asked for, once per device, with that device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxStaticDevices) return -TYR_ATTN_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return -TYR_ATTN_ERR_NO_DEVICE;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+}  // namespace tyr
+
+extern "C" int tyr_b200_attn_decode_static(const TyrAttnDecodeArgs* args, void* stream) {
+  using namespace tyr;
+  if (args == nullptr) return -TYR_ATTN_ERR_NULL;
+  if (args->batch <= 0 || args->n_head <= 0 || args->head_dim <= 0 || args->max_kv_seq <= 0)
+    return -TYR_ATTN_ERR_SHAPE;
+  const size_t need = decode_workspace_bytes(args->batch, args->n_head, args->head_dim,
+                                             args->max_kv_seq, args->max_splits);
+  if (need > kStaticScratchBytes) return -TYR_ATTN_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // Nothing in the scratch has to start at zero: the split kernel writes every
+  // (row, chunk) slot the merge kernel later reads, so stale contents of an
+  // earlier call are never observed.
+  TyrAttnDecodeArgs a = *args;
+  a.workspace = scratch;
+  a.workspace_bytes = kStaticScratchBytes;
+  return tyr_b200_attn_decode(&a, stream);
+}

@@ -208,6 +208,47 @@ def flashDecode(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] = None
     return out, lse
 
 
+def flashDecodeStatic(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] = None,
+                      out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None):
+    """`flashDecode` for callers that may not allocate device memory while decoding.
+
+    Some hosts of this operator cannot call cudaMalloc in their token loop: their
+    memory pool already owns the device, or an allocation's device-wide
+    synchronisation would stall the loop.  This call goes through
+    tyr_b200_attn_decode_static, which keeps the split-KV scratch in a fixed
+    16 MiB array inside the library instead of `plan.workspace`, so the library
+    allocates nothing; pass `out` and `lse` to keep this wrapper allocation-free too.
+    Shapes whose scratch would not fit raise AttnError (size beyond the supported
+    maximum).  All calls on one device share that array: keep them on one stream.
+    The first call on a device looks the array up and should come before any
+    stream capture.
+    """
+    q3 = q[:, :, 0, :] if q.dim() == 4 else q
+    _require_cuda(q3)
+    if q3.dtype != torch.bfloat16 or q3.shape != (plan.batch, plan.n_head, plan.head_dim):
+        raise ValueError("q must be bf16 [batch, n_head, head_dim]")
+    if out is None:
+        out = torch.empty((plan.batch, plan.n_head, plan.head_dim), dtype=q.dtype, device=q.device)
+    if lse is None:
+        lse = torch.empty((plan.batch, plan.n_head), dtype=torch.float32, device=q.device)
+    a = DecodeArgs()
+    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.k = a.v = None
+    a.k_ptrs, a.v_ptrs = plan.k_ptrs.data_ptr(), plan.v_ptrs.data_ptr()
+    a.kv_lens, a.kv_head_strides = plan.kv_lens.data_ptr(), plan.head_strides.data_ptr()
+    a.batch, a.n_head, a.n_kv_head = plan.batch, plan.n_head, plan.n_kv_head
+    a.max_kv_seq, a.head_dim = plan.max_kv_seq, plan.head_dim
+    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
+    a.o_stride[:] = [out.stride(0), out.stride(1)]
+    a.k_stride[:] = [0, 0, plan.head_dim]
+    a.v_stride[:] = [0, 0, plan.head_dim]
+    a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    a.workspace, a.workspace_bytes = None, 0      # ignored: the library's own array is used
+    with torch.cuda.device(q.device):
+        check(_lib.load().tyr_b200_attn_decode_static(ctypes.byref(a), _stream_ptr(q)))
+    return out, lse
+
+
 def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      kv_lens: Optional[torch.Tensor] = None, kv_len: Optional[int] = None,
                      scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
