@@ -22,6 +22,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "attn_internal.h"
@@ -54,7 +55,7 @@ struct Cfg {
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = kKOff + kKStages * kTileBytes;
   static constexpr uint32_t kBarOff = kVOff + kVStages * kTileBytes;
-  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2;
+  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2 + 2;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemO = 256;
@@ -75,6 +76,7 @@ struct Bars {
   static constexpr int p_full = s_full + 2;               // [2]
   static constexpr int o_full = p_full + 2;               // [2]
   static constexpr int e_full = o_full + 2;               // [2] epilogue rows staged in smem
+  static constexpr int p_half = e_full + 2;               // [2] first 64 keys of P_t written
 };
 
 template <int D>
@@ -91,19 +93,45 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint3
   }
 }
 
+// `half` selects keys [64*half, 64*half + 64) of the tile.
 template <int D>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem,
-                                         bool accumulate) {
+                                         bool accumulate, int half) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
 #pragma unroll
-  for (int kk = 0; kk < kBN / 16; ++kk) {
+  for (int k4 = 0; k4 < kBN / 32; ++k4) {
+    const int kk = half * (kBN / 32) + k4;
     // 16 keys = two 8-row groups of the V tile; 16 bf16 of P = 8 TMEM columns
     umma_ts(o_tmem, p_tmem + kk * 8, umma_smem_desc(v_smem + kk * 2048, Cfg<D>::kBoxBytes, 1024),
             idesc, (accumulate || kk != 0) ? 1u : 0u);
   }
 }
 
-template <int D>
+// exp2 of one 32-column chunk of a score row, packed to bf16x2, with the row sum.
+// kPoly of every 8 column pairs go through the FMA-pipe polynomial, the rest
+// through ex2.approx, so that neither unit alone bounds the softmax.
+template <int kPoly>
+__device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2x2, uint64_t negx2,
+                                          uint32_t (&pk)[16], uint64_t& sum_a, uint64_t& sum_b) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * i], sr[2 * i + 1]), sl2x2, negx2);
+    float p0, p1;
+    if ((i & 7) < kPoly) {
+      ex2_poly_x2(t2, p0, p1);
+    } else {
+      float t0, t1;
+      unpack_f32x2(t2, t0, t1);
+      p0 = ex2_approx(t0);
+      p1 = ex2_approx(t1);
+    }
+    if (i & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
+    else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+    pk[i] = pack_bf16x2(p0, p1);
+  }
+}
+
+template <int D, int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -131,7 +159,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), ((i >= B::p_full && i < B::p_full + 2) || i >= B::e_full) ? 128u : 1u);
+    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), ((i >= B::p_full && i < B::p_full + 2) || i >= B::e_full) ? 128u : 1u);  // p_full, e_full, p_half: one arrival per softmax thread
     mbar_fence_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
@@ -215,20 +243,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t v_smem = sV + vs * C::kTileBytes;
         const uint32_t k_smem = sK + ks * C::kTileBytes;
         if (j < n0) {
+          ok = mbar_wait(bar(B::p_half + 0), j & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv<D>(tO0, tS0, v_smem, j > 0, 0);
           ok = mbar_wait(bar(B::p_full + 0), j & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          issue_pv<D>(tO0, tS0, v_smem, j > 0);
+          issue_pv<D>(tO0, tS0, v_smem, true, 1);
           if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
         }
         if (j + 1 < n0) {
           issue_qk<D>(tS0, sQ, k_smem);
           umma_commit(bar(B::s_full + 0));
         }
+        ok = mbar_wait(bar(B::p_half + 1), j & 1, abortp);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv<D>(tO1, tS1, v_smem, j > 0, 0);
         ok = mbar_wait(bar(B::p_full + 1), j & 1, abortp);
         if (!ok) break;
         tc_fence_after();
-        issue_pv<D>(tO1, tS1, v_smem, j > 0);
+        issue_pv<D>(tO1, tS1, v_smem, true, 1);
         umma_commit(bar(B::v_empty + vs));
         if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
         if (next) {
@@ -272,9 +308,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int c = 0; c < kBN; ++c)
           if (c >= limit) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
       }
-      float mx = __uint_as_float(sr[0][0]);
+      float mxa[4];
 #pragma unroll
-      for (int c = 1; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
+      for (int c = 0; c < 4; ++c)
+        mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2)
+          mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+        mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
+      }
+      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
 
       const float m_new = fmaxf(m_ref, mx);
       if (j == 0) {
@@ -299,20 +344,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       const float neg = -m_ref * sl2;
-      float sum = 0.f;
+      const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
+      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
       for (int c = 0; c < kBN / 32; ++c) {
         uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i]), sl2, neg));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i + 1]), sl2, neg));
-          sum += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
+        exp_chunk<kPoly>(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
         tmem_st16(tS + c * 16, pk);
+        if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B::p_half + t));
+        }
       }
-      l += sum;
+      {
+        float s0, s1;
+        unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
+        l += s0 + s1;
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B::p_full + t));
@@ -422,7 +471,7 @@ int make_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int
   return r == CUDA_SUCCESS ? 0 : -TYR_ATTN_ERR_ALIGN;
 }
 
-template <int D>
+template <int D, int kPoly>
 int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv, to;
@@ -433,7 +482,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   if ((rc = make_map(&to, a.o, a.batch, a.n_head, a.q_seq, D, a.o_stride))) return rc;
   // per-device attribute: set on every launch so that any current device is covered
   cudaError_t attr_err = cudaFuncSetAttribute(
-      prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+      prefill_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
   if (attr_err != cudaSuccess) return (int)attr_err;
   PrefillParams p;
   p.lse = a.lse;
@@ -446,7 +495,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   dim3 grid((a.q_seq + 2 * kBM - 1) / (2 * kBM), a.n_head, a.batch);
-  prefill_kernel<D><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
+  prefill_kernel<D, kPoly><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -454,8 +503,17 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 }  // namespace
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
-  if (a.head_dim == 128) return launch<128>(a, scale, status, st);
-  if (a.head_dim == 64) return launch<64>(a, scale, status, st);
+  static const int poly = [] { const char* e = getenv("TYR_ATTN_POLY"); return e ? atoi(e) : 0; }();
+  if (a.head_dim == 128) {
+    switch (poly) {
+      case 0: return launch<128, 0>(a, scale, status, st);
+      case 1: return launch<128, 1>(a, scale, status, st);
+      case 3: return launch<128, 3>(a, scale, status, st);
+      case 4: return launch<128, 4>(a, scale, status, st);
+      default: return launch<128, 2>(a, scale, status, st);
+    }
+  }
+  if (a.head_dim == 64) return launch<64, 0>(a, scale, status, st);
   return -TYR_ATTN_ERR_HEAD_DIM;
 }
 

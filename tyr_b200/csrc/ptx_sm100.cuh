@@ -231,4 +231,70 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+
+// ---- packed fp32x2 arithmetic (one issue slot for two lanes of a row)
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void unpack_u32x2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^t for two values on the FMA pipe instead of the special-function unit:
+// n = round(t) taken from the mantissa of t + 1.5*2^23, f = t - n in [-0.5, 0.5],
+// cubic through the Chebyshev nodes of that interval (relative error 1.0e-4, below
+// the 3.9e-3 step of the bf16 value it is rounded to), then n added to the exponent.
+// t is clamped at -125 so the exponent never wraps; -inf gives 2^-125.
+__device__ __forceinline__ void ex2_poly_x2(uint64_t t2, float& p0, float& p1) {
+  float t0, t1;
+  unpack_f32x2(t2, t0, t1);
+  t0 = fmaxf(t0, -125.0f);
+  t1 = fmaxf(t1, -125.0f);
+  const uint64_t tc = pack_f32x2(t0, t1);
+  const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
+  const uint64_t nmagic = pack_f32x2(-12582912.0f, -12582912.0f);
+  const uint64_t r = add_f32x2(tc, magic);                  // low mantissa bits = round(t)
+  const uint64_t n = add_f32x2(r, nmagic);
+  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.0f, -1.0f), tc);
+  uint64_t p = fma_f32x2(pack_f32x2(0.05583828315f, 0.05583828315f), f,
+                         pack_f32x2(0.2426394820f, 0.2426394820f));
+  p = fma_f32x2(p, f, pack_f32x2(0.6931367517f, 0.6931367517f));
+  p = fma_f32x2(p, f, pack_f32x2(0.9999245405f, 0.9999245405f));
+  uint32_t pb0, pb1, rb0, rb1;
+  unpack_u32x2(p, pb0, pb1);
+  unpack_u32x2(r, rb0, rb1);
+  p0 = __uint_as_float(pb0 + (rb0 << 23));
+  p1 = __uint_as_float(pb1 + (rb1 << 23));
+}
+
 }  // namespace tyr
