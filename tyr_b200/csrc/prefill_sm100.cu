@@ -1,7 +1,8 @@
 // Flash-attention forward for sm_100a: TMA-staged Q/K/V tiles, tcgen05.mma with
 // fp32 accumulators in tensor memory for S = Q K^T and O += P V, online softmax
 // in the exp2 domain by two softmax warpgroups that each own one 128-row Q tile,
-// P handed back to the tensor core through tensor memory, O written by TMA store.
+// P handed back to the tensor core through tensor memory, O stored from registers.
+// Persistent: one CTA per SM loops over work items, longest causal rows first.
 //
 // Replaces, for bf16 CUDA tensors, the ATen call behind Tyr's typed attention
 // (cc/src/tyr.cpp:2578, 3941, 4126) and the SM90-only DSL kernels
@@ -9,7 +10,7 @@
 // follows Tyr/GPU/Codegen/Macros.lean:121-163: running max, running sum, rescale
 // of the output accumulator, LSE = log(rowSum) + rowMax of the scaled scores.
 //
-// One CTA = 256 query rows (two 128-row tiles) of one (batch, query head).
+// One work item = 256 query rows (two 128-row tiles) of one (batch, query head).
 //   warp 0     : TMA producer (one elected lane)
 //   warp 1     : tcgen05.mma issuer (one elected lane)
 //   warp 2     : tensor-memory allocation
@@ -22,6 +23,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -35,12 +37,22 @@ constexpr int kBM = 128;        // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;        // keys per KV tile
 constexpr int kThreads = 384;   // 12 warps
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
+// Register split.  setmaxnreg only moves registers inside what the CTA was given at
+// launch (threads x the compiled per-thread count, 168 under __launch_bounds__(384, 1));
+// asking for more would block a warp forever, so the sum is checked here.
+constexpr int kLaunchRegs = 168, kCtrlRegs = 88, kSoftmaxRegs = 208;
+static_assert(128 * kCtrlRegs + 256 * kSoftmaxRegs <= kThreads * kLaunchRegs, "register pool of the CTA");
 
 struct PrefillParams {
+  __nv_bfloat16* o;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
   float* lse;
   int64_t lse_stride_b, lse_stride_h;
   int q_seq, kv_seq, group, causal;
-  float scale_log2;  // scale * log2(e)
+  int n_head, batch, n_mblk;  // work items: n_mblk x n_head x batch
+  int n_kv_head, groups_per_chunk;  // (batch, KV head) groups whose K/V share L2 at one time
+  int snake;  // 1: odd rounds of the static schedule are mirrored
+  float scale_log2;           // scale * log2(e)
   int* status;
 };
 
@@ -55,7 +67,7 @@ struct Cfg {
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = kKOff + kKStages * kTileBytes;
   static constexpr uint32_t kBarOff = kVOff + kVStages * kTileBytes;
-  static constexpr int kNumBars = 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2 + 2;
+  static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemO = 256;
@@ -67,17 +79,63 @@ struct Cfg {
 template <int D>
 struct Bars {
   using C = Cfg<D>;
-  static constexpr int q_full = 0;                        // [2]
-  static constexpr int k_full = 2;                        // [KS]
+  static constexpr int q_full = 0;                        // [2] Q_t of the current item landed
+  static constexpr int q_empty = 2;                       // [2] last S_t of the item has read Q_t
+  static constexpr int k_full = 4;                        // [KS]
   static constexpr int k_empty = k_full + C::kKStages;    // [KS]
   static constexpr int v_full = k_empty + C::kKStages;    // [VS]
   static constexpr int v_empty = v_full + C::kVStages;    // [VS]
-  static constexpr int s_full = v_empty + C::kVStages;    // [2]
-  static constexpr int p_full = s_full + 2;               // [2]
-  static constexpr int o_full = p_full + 2;               // [2]
-  static constexpr int e_full = o_full + 2;               // [2] epilogue rows staged in smem
-  static constexpr int p_half = e_full + 2;               // [2] first 64 keys of P_t written
+  static constexpr int s_full = v_empty + C::kVStages;    // [2] S_t in tensor memory
+  static constexpr int p_half = s_full + 2;               // [2] keys 0..63 of P_t written
+  static constexpr int p_full = p_half + 2;               // [2] keys 64..127 of P_t written
+  static constexpr int o_full = p_full + 2;               // [2] last PV_t of the item done
+  __device__ static constexpr uint32_t count(int i) {
+    return (i >= p_half && i < p_half + 4) ? 4u : 1u;     // one arrival per softmax warp
+  }
 };
+
+// One work item = 256 query rows of one (batch, query head).  Item order: the
+// (batch, KV head) groups are cut into chunks whose K/V fit in L2 together; inside a
+// chunk the longest causal rows come first (so the static round-robin over CTAs stays
+// balanced and the light items fill the tail), and the query heads that share a KV
+// head are neighbours, so CTAs running at the same time read the same K/V tiles.
+struct Item {
+  int mblk, hq, b, hkv, row0, n0, n1;
+};
+__device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
+  Item it;
+  const int n_groups = p.batch * p.n_kv_head;
+  const int items_per_group = p.n_mblk * p.group;
+  const int chunk = w / (p.groups_per_chunk * items_per_group);
+  const int within = w - chunk * p.groups_per_chunk * items_per_group;
+  const int g0 = chunk * p.groups_per_chunk;
+  const int groups_here = min(p.groups_per_chunk, n_groups - g0);
+  const int per_level = groups_here * p.group;
+  it.mblk = p.n_mblk - 1 - within / per_level;
+  const int idx = within % per_level;
+  const int gi = g0 + idx / p.group;
+  it.b = gi / p.n_kv_head;
+  it.hkv = gi % p.n_kv_head;
+  it.hq = it.hkv * p.group + idx % p.group;
+  it.row0 = it.mblk * 2 * kBM;
+  const int nkv_total = (p.kv_seq + kBN - 1) / kBN;
+  // KV tiles each Q tile visits.  Top-left causal: tile m needs keys <= its last row.
+  it.n0 = p.causal ? min(nkv_total, 2 * it.mblk + 1) : nkv_total;
+  it.n1 = p.causal ? min(nkv_total, 2 * it.mblk + 2) : nkv_total;
+  return it;
+}
+
+// Static schedule: in round `it` CTA c takes item it*G + c; with `snake` odd rounds
+// are mirrored (G-1-c), so that with costs falling along the item order every CTA
+// gets the same mix of long and short items.  -1 when the CTA has no item in this round
+// (which can only be its last round).
+__device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
+  const int G = gridDim.x;
+  const int c = ((it & 1) && snake) ? (G - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const long long w = (long long)it * G + c;
+  if ((long long)it * G >= total_items) return -1;
+  return w < total_items ? (int)w : -2;
+}
 
 template <int D>
 __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem) {
@@ -109,7 +167,7 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint3
 
 // exp2 of one 32-column chunk of a score row, packed to bf16x2, with the row sum.
 // kPoly of every 8 column pairs go through the FMA-pipe polynomial, the rest
-// through ex2.approx, so that neither unit alone bounds the softmax.
+// through ex2.approx.
 template <int kPoly>
 __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2x2, uint64_t negx2,
                                           uint32_t (&pk)[16], uint64_t& sum_a, uint64_t& sum_b) {
@@ -131,11 +189,14 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
   }
 }
 
+// Persistent kernel: CTA c works on items c, c + gridDim.x, ...  Barrier phases
+// run on across items (every role counts its own uses), tensor memory and the
+// barriers are set up once, the next item's Q/K loads and first QK^T overlap the
+// previous item's epilogue.
 template <int D, int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               const PrefillParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
   using C = Cfg<D>;
   using B = Bars<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -149,22 +210,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mblk = gridDim.x - 1 - blockIdx.x;  // causal: longest rows first
-  const int hq = blockIdx.y, b = blockIdx.z, hkv = hq / p.group;
-  const int row0 = mblk * 2 * kBM;
-  const int nkv_total = (p.kv_seq + kBN - 1) / kBN;
-  // KV tiles each Q tile visits.  Top-left causal: tile m needs keys <= its last row.
-  const int n0 = p.causal ? min(nkv_total, 2 * mblk + 1) : nkv_total;
-  const int n1 = p.causal ? min(nkv_total, 2 * mblk + 2) : nkv_total;
+  const int total_items = p.n_mblk * p.n_head * p.batch;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), ((i >= B::p_full && i < B::p_full + 2) || i >= B::e_full) ? 128u : 1u);  // p_full, e_full, p_half: one arrival per softmax thread
+    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), B::count(i));
     mbar_fence_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    tma_prefetch_desc(&tm_o);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
@@ -179,203 +233,242 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // Register budget: the four warps of the first warpgroup only issue copies and
   // MMAs; the softmax warpgroups hold a whole 128-column score row per thread.
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      bool ok = true;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCtrlRegs));
+    if (warp == 0) {
+      // ---------------------------------------------------------- producer
+      if (lane == 0) {
+        bool ok = true;
+        int kc = 0, vc = 0;  // K / V tiles loaded so far, over all items
+        for (int it = 0; ok; ++it) {
+          const int w = snake_item(it, total_items, p.snake);
+          if (w < 0) break;
+          const Item im = decode_item(w, p);
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        mbar_expect_tx(bar(B::q_full + t), C::kTileBytes);
+          for (int t = 0; t < 2; ++t) {
+            if (it > 0) ok = ok && mbar_wait(bar(B::q_empty + t), (it - 1) & 1, abortp);
+            if (!ok) break;
+            mbar_expect_tx(bar(B::q_full + t), C::kTileBytes);
 #pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_load_4d(sQ + t * C::kTileBytes + kb * C::kBoxBytes, &tm_q, bar(B::q_full + t), kb * 64,
-                      row0 + t * kBM, hq, b);
+            for (int kb = 0; kb < C::kBoxes; ++kb)
+              tma_load_4d(sQ + t * C::kTileBytes + kb * C::kBoxBytes, &tm_q, bar(B::q_full + t), kb * 64,
+                          im.row0 + t * kBM, im.hq, im.b);
+          }
+          auto load_k = [&](int j) {
+            const int s = kc % C::kKStages;
+            if (kc >= C::kKStages) ok = ok && mbar_wait(bar(B::k_empty + s), ((kc / C::kKStages) - 1) & 1, abortp);
+            if (!ok) return;
+            mbar_expect_tx(bar(B::k_full + s), C::kTileBytes);
+#pragma unroll
+            for (int kb = 0; kb < C::kBoxes; ++kb)
+              tma_load_4d(sK + s * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(B::k_full + s), kb * 64,
+                          j * kBN, im.hkv, im.b);
+            ++kc;
+          };
+          auto load_v = [&](int j) {
+            const int s = vc % C::kVStages;
+            if (vc >= C::kVStages) ok = ok && mbar_wait(bar(B::v_empty + s), ((vc / C::kVStages) - 1) & 1, abortp);
+            if (!ok) return;
+            mbar_expect_tx(bar(B::v_full + s), C::kTileBytes);
+#pragma unroll
+            for (int kb = 0; kb < C::kBoxes; ++kb)
+              tma_load_4d(sV + s * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(B::v_full + s), kb * 64,
+                          j * kBN, im.hkv, im.b);
+            ++vc;
+          };
+          if (ok) load_k(0);
+          for (int j = 0; j < im.n1 && ok; ++j) {
+            if (j + 1 < im.n1) load_k(j + 1);
+            load_v(j);
+          }
+        }
       }
-      auto load_k = [&](int j) {
-        const int s = j % C::kKStages;
-        if (j >= C::kKStages) ok = ok && mbar_wait(bar(B::k_empty + s), ((j / C::kKStages) - 1) & 1, abortp);
-        if (!ok) return;
-        mbar_expect_tx(bar(B::k_full + s), C::kTileBytes);
-#pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_load_4d(sK + s * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(B::k_full + s), kb * 64,
-                      j * kBN, hkv, b);
-      };
-      auto load_v = [&](int j) {
-        const int s = j % C::kVStages;
-        if (j >= C::kVStages) ok = ok && mbar_wait(bar(B::v_empty + s), ((j / C::kVStages) - 1) & 1, abortp);
-        if (!ok) return;
-        mbar_expect_tx(bar(B::v_full + s), C::kTileBytes);
-#pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_load_4d(sV + s * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(B::v_full + s), kb * 64,
-                      j * kBN, hkv, b);
-      };
-      load_k(0);
-      for (int j = 0; j < n1 && ok; ++j) {
-        if (j + 1 < n1) load_k(j + 1);
-        load_v(j);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t tS0 = tmem + C::kTmemS, tS1 = tS0 + kBN;
-      const uint32_t tO0 = tmem + C::kTmemO, tO1 = tO0 + D;
-      bool ok = mbar_wait(bar(B::q_full + 0), 0, abortp) && mbar_wait(bar(B::q_full + 1), 0, abortp) &&
-                mbar_wait(bar(B::k_full + 0), 0, abortp);
-      if (ok) {
-        tc_fence_after();
-        issue_qk<D>(tS0, sQ, sK);
-        umma_commit(bar(B::s_full + 0));
-        issue_qk<D>(tS1, sQ + C::kTileBytes, sK);
-        umma_commit(bar(B::s_full + 1));
-        umma_commit(bar(B::k_empty + 0));
-      }
-      for (int j = 0; j < n1 && ok; ++j) {
-        const int vs = j % C::kVStages;
-        const bool next = (j + 1 < n1);
-        const int ks = (j + 1) % C::kKStages;
-        ok = mbar_wait(bar(B::v_full + vs), (j / C::kVStages) & 1, abortp);
-        if (ok && next) ok = mbar_wait(bar(B::k_full + ks), ((j + 1) / C::kKStages) & 1, abortp);
-        if (!ok) break;
-        const uint32_t v_smem = sV + vs * C::kTileBytes;
-        const uint32_t k_smem = sK + ks * C::kTileBytes;
-        if (j < n0) {
-          ok = mbar_wait(bar(B::p_half + 0), j & 1, abortp);
+    } else if (warp == 1) {
+      // -------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        const uint32_t tS0 = tmem + C::kTmemS, tS1 = tS0 + kBN;
+        const uint32_t tO0 = tmem + C::kTmemO, tO1 = tO0 + D;
+        bool ok = true;
+        int kc = 0, vc = 0;      // K / V tiles consumed so far
+        int pc0 = 0, pc1 = 0;    // P tiles consumed so far, per Q tile
+        for (int it = 0; ok; ++it) {
+          const int w = snake_item(it, total_items, p.snake);
+          if (w < 0) break;
+          const Item im = decode_item(w, p);
+          const int n0 = im.n0, n1 = im.n1;
+          ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
+               mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          issue_pv<D>(tO0, tS0, v_smem, j > 0, 0);
-          ok = mbar_wait(bar(B::p_full + 0), j & 1, abortp);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv<D>(tO0, tS0, v_smem, true, 1);
-          if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
-        }
-        if (j + 1 < n0) {
-          issue_qk<D>(tS0, sQ, k_smem);
-          umma_commit(bar(B::s_full + 0));
-        }
-        ok = mbar_wait(bar(B::p_half + 1), j & 1, abortp);
-        if (!ok) break;
-        tc_fence_after();
-        issue_pv<D>(tO1, tS1, v_smem, j > 0, 0);
-        ok = mbar_wait(bar(B::p_full + 1), j & 1, abortp);
-        if (!ok) break;
-        tc_fence_after();
-        issue_pv<D>(tO1, tS1, v_smem, true, 1);
-        umma_commit(bar(B::v_empty + vs));
-        if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
-        if (next) {
-          issue_qk<D>(tS1, sQ + C::kTileBytes, k_smem);
-          umma_commit(bar(B::s_full + 1));
-          umma_commit(bar(B::k_empty + ks));
+          {
+            const int s = kc % C::kKStages;
+            issue_qk<D>(tS0, sQ, sK + s * C::kTileBytes);
+            umma_commit(bar(B::s_full + 0));
+            if (n0 == 1) umma_commit(bar(B::q_empty + 0));
+            issue_qk<D>(tS1, sQ + C::kTileBytes, sK + s * C::kTileBytes);
+            umma_commit(bar(B::s_full + 1));
+            if (n1 == 1) umma_commit(bar(B::q_empty + 1));
+            umma_commit(bar(B::k_empty + s));
+            ++kc;
+          }
+          for (int j = 0; j < n1 && ok; ++j) {
+            const int vs = vc % C::kVStages;
+            const bool next = (j + 1 < n1);
+            const int ks = kc % C::kKStages;
+            ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
+            if (ok && next) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
+            if (!ok) break;
+            const uint32_t v_smem = sV + vs * C::kTileBytes;
+            const uint32_t k_smem = sK + ks * C::kTileBytes;
+            if (j < n0) {
+              ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv<D>(tO0, tS0, v_smem, j > 0, 0);
+              ok = mbar_wait(bar(B::p_full + 0), pc0 & 1, abortp);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv<D>(tO0, tS0, v_smem, true, 1);
+              ++pc0;
+              if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
+            }
+            if (j + 1 < n0) {
+              issue_qk<D>(tS0, sQ, k_smem);
+              umma_commit(bar(B::s_full + 0));
+              if (j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
+            }
+            ok = mbar_wait(bar(B::p_half + 1), pc1 & 1, abortp);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv<D>(tO1, tS1, v_smem, j > 0, 0);
+            ok = mbar_wait(bar(B::p_full + 1), pc1 & 1, abortp);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv<D>(tO1, tS1, v_smem, true, 1);
+            ++pc1;
+            umma_commit(bar(B::v_empty + vs));
+            ++vc;
+            if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
+            if (next) {
+              issue_qk<D>(tS1, sQ + C::kTileBytes, k_smem);
+              umma_commit(bar(B::s_full + 1));
+              if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
+              umma_commit(bar(B::k_empty + ks));
+              ++kc;
+            }
+          }
         }
       }
     }
-  }
   } else {
-    // --------------------------------------------------- softmax + epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // ------------------------------------------------- softmax + epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int t = (warp - 4) >> 2;          // Q tile of this warpgroup
     const int quarter = warp & 3;           // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;      // row within the tile = TMEM lane
-    const int row = row0 + t * kBM + r;     // query index
-    const int n_t = t ? n1 : n0;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + C::kTmemS + t * kBN;
     const uint32_t tO = tmem + lane_addr + C::kTmemO + t * D;
     const float sl2 = p.scale_log2;
-    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    int sc = 0;  // score tiles of this Q-tile slot processed so far, over all items
 
-    for (int j = 0; j < n_t; ++j) {
-      ok = mbar_wait(bar(B::s_full + t), j & 1, abortp);
+    for (int it = 0; ok; ++it) {
+      const int w = snake_item(it, total_items, p.snake);
+      if (w < 0) break;
+      const Item im = decode_item(w, p);
+      const int row = im.row0 + t * kBM + r;  // query index
+      const int n_t = t ? im.n1 : im.n0;
+      float m_ref = -INFINITY, l = 0.f;
+
+      for (int j = 0; j < n_t; ++j, ++sc) {
+        ok = mbar_wait(bar(B::s_full + t), sc & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[kBN / 32][32];  // the row's scores, raw fp32 bits
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, sr[c]);
+        tmem_wait_ld();
+
+        // keys this row may see in this tile: [0, limit)
+        int limit = p.kv_seq - j * kBN;
+        if (p.causal) limit = min(limit, row + 1 - j * kBN);
+        if (limit < kBN) {
+#pragma unroll
+          for (int c = 0; c < kBN; ++c)
+            if (c >= limit) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+        }
+        float mxa[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 3; i + 1 < 32; i += 2)
+            mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+          mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
+        }
+        const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+
+        const float m_new = fmaxf(m_ref, mx);
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          const bool grow = (m_new - m_ref) * sl2 > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            // PV_t(j-1) has completed (s_full covers it) and PV_t(j) is not issued
+            // before this warp arrives on p_half, so O_t is ours to rescale.
+            const float alpha = ex2_approx((m_ref - m_new) * sl2);
+            l *= alpha;
+            m_ref = m_new;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + c * 32, o);
+            }
+          }
+        }
+        const float neg = -m_ref * sl2;
+        const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
+        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t pk[16];
+          exp_chunk<kPoly>(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
+          tmem_st16(tS + c * 16, pk);
+          if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B::p_half + t));
+          }
+        }
+        {
+          float s0, s1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
+          l += s0 + s1;
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B::p_full + t));
+      }
+      if (!ok) break;
+
+      // epilogue: O_t / l -> bf16 -> global, straight from registers (each thread owns
+      // one row; its 16-byte stores fill whole 32-byte sectors pairwise)
+      ok = mbar_wait(bar(B::o_full + t), it & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[kBN / 32][32];  // the row's scores, raw fp32 bits
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, sr[c]);
-      tmem_wait_ld();
-
-      // keys this row may see in this tile: [0, limit)
-      int limit = p.kv_seq - j * kBN;
-      if (p.causal) limit = min(limit, row + 1 - j * kBN);
-      if (limit < kBN) {
-#pragma unroll
-        for (int c = 0; c < kBN; ++c)
-          if (c >= limit) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
-      }
-      float mxa[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 3; i + 1 < 32; i += 2)
-          mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-        mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
-      }
-      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
-
-      const float m_new = fmaxf(m_ref, mx);
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        const bool grow = (m_new - m_ref) * sl2 > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, grow)) {
-          // PV_t(j-1) has completed (s_full covers it) and PV_t(j) is not issued
-          // before this thread arrives on p_full, so O_t is ours to rescale.
-          const float alpha = ex2_approx((m_ref - m_new) * sl2);
-          l *= alpha;
-          m_ref = m_new;
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + c * 32, o);
-          }
-        }
-      }
-      const float neg = -m_ref * sl2;
-      const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
-      uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t pk[16];
-        exp_chunk<kPoly>(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
-        tmem_st16(tS + c * 16, pk);
-        if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar(B::p_half + t));
-        }
-      }
-      {
-        float s0, s1;
-        unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
-        l += s0 + s1;
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(B::p_full + t));
-    }
-
-    // epilogue: O_t / l -> bf16 -> swizzled smem (the Q tile's buffer) -> TMA store
-    if (ok) {
-      ok = mbar_wait(bar(B::o_full + t), 0, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
       const float inv_l = 1.0f / l;
-      const uint32_t sO = sQ + t * C::kTileBytes;
+      const bool row_ok = row < p.q_seq;
+      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + im.hq * p.o_stride_h + (int64_t)row * p.o_stride_s;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -383,31 +476,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tmem_wait_ld();
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            w[i] = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2 * i]) * inv_l,
-                               __uint_as_float(o[q4 * 8 + 2 * i + 1]) * inv_l);
-          const int chunk = c * 4 + q4;  // 16-byte chunk of the row
-          const uint32_t addr = sO + (chunk >> 3) * C::kBoxBytes + r * 128 +
-                                (((chunk & 7) ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
-                       "r"(w[2]), "r"(w[3])
-                       : "memory");
+          uint4 wv;
+          wv.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv_l, __uint_as_float(o[q4 * 8 + 1]) * inv_l);
+          wv.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
+          wv.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
+          wv.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
+          if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = wv;
         }
       }
-      if (p.lse != nullptr && row < p.q_seq)
-        p.lse[b * p.lse_stride_b + hq * p.lse_stride_h + row] =
+      if (p.lse != nullptr && row_ok)
+        p.lse[im.b * p.lse_stride_b + im.hq * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
-      fence_proxy_async_smem();
-      mbar_arrive(bar(B::e_full + t));
-      if (r == 0 && row0 + t * kBM < p.q_seq && mbar_wait(bar(B::e_full + t), 0, abortp)) {
-#pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_store_4d(&tm_o, sO + kb * C::kBoxBytes, kb * 64, row0 + t * kBM, hq, b);
-        tma_store_commit();
-        tma_store_wait_read0();
-      }
+      // O_t is read: order these loads before the next item's first PV_t, which this
+      // warp gates through p_half
+      tc_fence_before();
     }
   }
 
@@ -471,20 +553,50 @@ int make_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int
   return r == CUDA_SUCCESS ? 0 : -TYR_ATTN_ERR_ALIGN;
 }
 
+// SMs of the current device (one persistent CTA each)
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  static int cache[64] = {0};
+  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < 64) cache[dev] = n;
+  return n;
+}
+
 template <int D, int kPoly>
 int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   using C = Cfg<D>;
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_map(&tq, a.q, a.batch, a.n_head, a.q_seq, D, a.q_stride))) return rc;
   if ((rc = make_map(&tk, a.k, a.batch, a.n_kv_head, a.kv_seq, D, a.k_stride))) return rc;
   if ((rc = make_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
-  if ((rc = make_map(&to, a.o, a.batch, a.n_head, a.q_seq, D, a.o_stride))) return rc;
   // per-device attribute: set on every launch so that any current device is covered
   cudaError_t attr_err = cudaFuncSetAttribute(
       prefill_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
   if (attr_err != cudaSuccess) return (int)attr_err;
   PrefillParams p;
+  p.o = static_cast<__nv_bfloat16*>(a.o);
+  p.o_stride_b = a.o_stride[0];
+  p.o_stride_h = a.o_stride[1];
+  p.o_stride_s = a.o_stride[2];
+  p.n_head = a.n_head;
+  p.batch = a.batch;
+  p.n_mblk = (a.q_seq + 2 * kBM - 1) / (2 * kBM);
+  p.n_kv_head = a.n_kv_head;
+  {
+    // K and V of one (batch, KV head) group.  If all groups fit in L2 together (96 MB of
+    // the 126 MB) the items form one chunk and the mirrored schedule balances the few
+    // rounds each CTA runs; otherwise chunks of about 48 MB keep the CTAs that run at
+    // the same time on K/V that is still in L2, and plain round-robin keeps them close.
+    const long long group_bytes = std::max<long long>(2ll * a.kv_seq * D * 2, 1);
+    const long long n_groups = (long long)a.batch * a.n_kv_head;
+    const bool all_fit = group_bytes * n_groups <= (96ll << 20);
+    const long long g = all_fit ? n_groups : std::max<long long>((48ll << 20) / group_bytes, 1);
+    p.groups_per_chunk = (int)std::min<long long>(g, n_groups);
+    p.snake = all_fit ? 1 : 0;
+  }
   p.lse = a.lse;
   p.lse_stride_h = a.q_seq;
   p.lse_stride_b = (int64_t)a.q_seq * a.n_head;
@@ -494,8 +606,10 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.causal = a.is_causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  dim3 grid((a.q_seq + 2 * kBM - 1) / (2 * kBM), a.n_head, a.batch);
-  prefill_kernel<D, kPoly><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
+  const long long items = (long long)p.n_mblk * a.n_head * a.batch;
+  if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
+  const int grid = (int)std::min<long long>(items, sm_count());
+  prefill_kernel<D, kPoly><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -503,16 +617,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 }  // namespace
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
-  static const int poly = [] { const char* e = getenv("TYR_ATTN_POLY"); return e ? atoi(e) : 0; }();
-  if (a.head_dim == 128) {
-    switch (poly) {
-      case 0: return launch<128, 0>(a, scale, status, st);
-      case 1: return launch<128, 1>(a, scale, status, st);
-      case 3: return launch<128, 3>(a, scale, status, st);
-      case 4: return launch<128, 4>(a, scale, status, st);
-      default: return launch<128, 2>(a, scale, status, st);
-    }
-  }
+  if (a.head_dim == 128) return launch<128, 0>(a, scale, status, st);
   if (a.head_dim == 64) return launch<64, 0>(a, scale, status, st);
   return -TYR_ATTN_ERR_HEAD_DIM;
 }
