@@ -170,6 +170,38 @@ int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, 
                         float* o_out, float* lse_out, int64_t rows, int32_t head_dim, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Fused prologue: per-head RMSNorm, rotary embedding, layout change and (for K/V)
+ * in-place append to the KV cache, for one projected tensor in one pass.
+ * Replaces the elementwise chain before every attention call of Tyr's models:
+ * applyHeadNorm (Tyr/Model/Qwen/Attention.lean:73-98), rotary.applyRotaryEmb
+ * (cc/src/tyr.cpp:3824-3861), transpose_for_attention (cc/src/tyr.cpp:2402-2414)
+ * and, in decode, data.sliceScatter's clone of the whole cache
+ * (cc/src/tyr.cpp:2261-2277; call site Tyr/Model/Qwen/Attention.lean:189-193).
+ *
+ *   y = x * rsqrt(mean(x^2) + eps) * norm_weight          (skipped when norm_weight == NULL)
+ *   [y1, y2] -> [y1*cos - y2*sin, y1*sin + y2*cos]         (skipped when cos == NULL)
+ *   out[b, h, pos_b + s, :] = bf16(y)      with pos_b = positions ? positions[b] : position0
+ * cos/sin: fp32 [max_pos, head_dim/2] indexed by pos_b + s.  head_dim in {64,128,256}.
+ * For Q pass position0 = rotary offset and an out tensor whose row 0 is that offset
+ * (out pointer already shifted); for K/V pass the cache and the sequence lengths.
+ * ---------------------------------------------------------------------- */
+typedef struct TyrAttnPrologueArgs {
+  const void* x;            /* [batch, seq, n_head, head_dim] bf16 */
+  void* out;                /* [batch, n_head, cap, head_dim] bf16 */
+  const float* norm_weight; /* [head_dim] fp32 or NULL */
+  const float* cos;         /* [max_pos, head_dim/2] fp32 or NULL */
+  const float* sin;
+  const int32_t* positions; /* DEVICE int32[batch] or NULL */
+  int32_t position0;
+  int32_t batch, seq, n_head, head_dim;
+  int64_t x_stride[3];      /* elements: batch, seq, head */
+  int64_t out_stride[3];    /* elements: batch, head, seq */
+  float eps;
+} TyrAttnPrologueArgs;
+
+int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------
  * Host-buffer call: same arithmetic as tyr_b200_attn_prefill, but every
  * pointer in `args` is HOST memory (pinned or pageable).  Copies Q/K/V to the
  * device, runs the kernel, copies O (and LSE) back and synchronises.  This is

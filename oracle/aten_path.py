@@ -38,3 +38,25 @@ def lse(q, k, v, is_causal: bool):
         v = v.repeat_interleave(rep, 1)
     out = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, 0.0, is_causal)
     return out[1]
+
+
+def head_norm_rope_transpose(x, weight=None, cos=None, sin=None, eps: float = 1e-6):
+    """The op chain Tyr runs on a projected [B,S,H,D] tensor before attention:
+    applyHeadNorm (Tyr/Model/Qwen/Attention.lean:73-98), rotary.applyRotaryEmb
+    (cc/src/tyr.cpp:3824-3861) and transpose_for_attention (cc/src/tyr.cpp:2402-2414)."""
+    if weight is not None:
+        var = (x * x).mean(-1, keepdim=True)
+        x = x * torch.rsqrt(var + eps) * weight.reshape(1, 1, 1, -1)
+    if cos is not None:
+        d = x.shape[3] // 2
+        x1, x2 = x[..., :d], x[..., d:]
+        cb, sb = cos.unsqueeze(0).unsqueeze(2), sin.unsqueeze(0).unsqueeze(2)
+        x = torch.cat([x1 * cb - x2 * sb, x1 * sb + x2 * cb], 3)
+    return x.permute(0, 2, 1, 3).contiguous()
+
+
+def slice_scatter_seq(cache, start: int, src):
+    """data.sliceScatter along the sequence axis (cc/src/tyr.cpp:2261-2277): a new cache."""
+    out = cache.clone()
+    out[:, :, start:start + src.shape[2]].copy_(src)
+    return out

@@ -183,3 +183,46 @@ void tyr_oracle_merge2(const float* o_a, const float* lse_a, const float* o_b, c
     lse_out[r] = (float)L;
   }
 }
+
+/* Prologue of the attention call on fp32 data, per (batch, token, head) row:
+ *   RMSNorm over the head vector, x * rsqrt(mean(x^2) + eps) * weight
+ *     (applyHeadNorm, Tyr/Model/Qwen/Attention.lean:73-98); skipped when weight == NULL;
+ *   rotary embedding on the two halves of the vector,
+ *     [x1, x2] -> [x1*cos - x2*sin, x1*sin + x2*cos] with cos/sin rows indexed by position
+ *     (lean_torch_apply_rotary_emb, cc/src/tyr.cpp:3824-3861); skipped when cos == NULL;
+ *   the layout change [B,S,H,D] -> [B,H,S,D] (transpose_for_attention, cc/src/tyr.cpp:2402-2414)
+ *   written at row positions[b] + s of out [B,H,cap,D], which for a KV cache is the
+ *   slice_scatter of the new rows (cc/src/tyr.cpp:2261-2277) done in place. */
+void tyr_oracle_qk_prologue(const float* x, const float* weight, const float* cs, const float* sn,
+                            const int32_t* positions, int position0, float* out, int B, int S, int H,
+                            int D, int cap, float eps) {
+  const int half = D / 2;
+  for (int b = 0; b < B; ++b)
+    for (int s = 0; s < S; ++s)
+      for (int h = 0; h < H; ++h) {
+        const float* xr = x + (((int64_t)b * S + s) * H + h) * D;
+        const int pos = (positions ? positions[b] : position0) + s;
+        float* orow = out + (((int64_t)b * H + h) * cap + pos) * D;
+        double inv = 1.0;
+        if (weight) {
+          double ss = 0.0;
+          for (int d = 0; d < D; ++d) ss += (double)xr[d] * xr[d];
+          inv = 1.0 / sqrt(ss / D + (double)eps);
+        }
+        for (int i = 0; i < half; ++i) {
+          double a = xr[i], c = xr[half + i];
+          if (weight) {
+            a *= inv * weight[i];
+            c *= inv * weight[half + i];
+          }
+          if (cs) {
+            const double co = cs[(int64_t)pos * half + i], si = sn[(int64_t)pos * half + i];
+            const double y1 = a * co - c * si, y2 = a * si + c * co;
+            a = y1;
+            c = y2;
+          }
+          orow[i] = (float)a;
+          orow[half + i] = (float)c;
+        }
+      }
+}

@@ -35,6 +35,9 @@ def lib() -> ctypes.CDLL:
         L.tyr_oracle_merge2.restype = None
         L.tyr_oracle_bf16_round.argtypes = [f32p, f32p, ctypes.c_int64]
         L.tyr_oracle_bf16_round.restype = None
+        i32p = ctypes.POINTER(ctypes.c_int32)
+        L.tyr_oracle_qk_prologue.argtypes = [f32p, f32p, f32p, f32p, i32p, ctypes.c_int, f32p] + [ctypes.c_int] * 5 + [ctypes.c_float]
+        L.tyr_oracle_qk_prologue.restype = None
         L.tyr_oracle_threads.restype = ctypes.c_int
         L.tyr_oracle_set_threads.argtypes = [ctypes.c_int]
         _lib = L
@@ -87,4 +90,23 @@ def bf16_round(x) -> np.ndarray:
     x = _c(x)
     out = np.empty_like(x)
     lib().tyr_oracle_bf16_round(_p(x), _p(out), x.size)
+    return out
+
+
+def qk_prologue(x, out, weight=None, cos=None, sin=None, positions=None, position0=0, eps=1e-6):
+    """x [B,S,H,D] fp32; out [B,H,cap,D] fp32 is updated in place and returned."""
+    x = _c(x)
+    assert out.dtype == np.float32 and out.flags["C_CONTIGUOUS"]
+    B, S, H, D = x.shape
+    cap = out.shape[2]
+    null = ctypes.POINTER(ctypes.c_float)()
+    w = _c(weight) if weight is not None else None
+    cs = _c(cos) if cos is not None else None
+    sn = _c(sin) if sin is not None else None
+    pos = np.ascontiguousarray(positions, dtype=np.int32) if positions is not None else None
+    lib().tyr_oracle_qk_prologue(
+        _p(x), _p(w) if w is not None else null, _p(cs) if cs is not None else null,
+        _p(sn) if sn is not None else null,
+        pos.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)) if pos is not None else ctypes.POINTER(ctypes.c_int32)(),
+        int(position0), _p(out), B, S, H, D, cap, float(eps))
     return out

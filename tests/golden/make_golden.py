@@ -56,5 +56,27 @@ def main():
     print(path, os.path.getsize(path), "bytes")
 
 
+def main_prologue():
+    """tests/golden/aten_prologue.npz: the reference's op chain before attention (per-head
+    RMSNorm, rotary embedding, transpose, cache slice_scatter) run with torch on fp32."""
+    g = torch.Generator(device="cpu").manual_seed(2000)
+    B, S, H, D, cap, start = 2, 3, 2, 128, 16, 5
+    x = torch.randn(B, S, H, D, generator=g).bfloat16().float()
+    w = (torch.rand(D, generator=g) + 0.5)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, D // 2).float() / (D // 2)))
+    ang = torch.arange(cap).float()[:, None] * inv_freq[None]
+    cos, sin = ang.cos(), ang.sin()
+    y = aten_path.head_norm_rope_transpose(x, w, cos[start:start + S], sin[start:start + S], 1e-6)
+    cache = torch.randn(B, H, cap, D, generator=g).bfloat16().float()
+    new_cache = aten_path.slice_scatter_seq(cache, start, y)
+    out = {"x": x.numpy(), "w": w.numpy(), "cos": cos.numpy(), "sin": sin.numpy(),
+           "cache": cache.numpy(), "new_cache": new_cache.numpy(), "start": np.array(start),
+           "torch_version": np.array(torch.__version__)}
+    path = os.path.join(os.path.dirname(__file__), "aten_prologue.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
+    main_prologue()

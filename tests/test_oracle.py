@@ -111,3 +111,37 @@ def test_oracle_rejects_bad_shapes():
     k = np.zeros((1, 2, 2, 8), np.float32)
     with pytest.raises(ValueError):
         c_oracle.sdpa(q, k, k, False)
+
+
+def test_prologue_oracle_matches_golden_reference_chain():
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_prologue.npz"))
+    cache = g["cache"].copy()
+    start = int(g["start"])
+    c_oracle.qk_prologue(g["x"], cache, g["w"], g["cos"], g["sin"], position0=start)
+    assert rel(cache, g["new_cache"]) < 1e-6
+    # rows outside [start, start + S) are the old cache, bit for bit
+    S = g["x"].shape[1]
+    keep = np.ones(cache.shape[2], bool)
+    keep[start:start + S] = False
+    np.testing.assert_array_equal(cache[:, :, keep], g["cache"][:, :, keep])
+
+
+def test_prologue_oracle_parts():
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((1, 2, 2, 64), dtype=np.float32)
+    out = np.zeros((1, 2, 4, 64), np.float32)
+    c_oracle.qk_prologue(x, out, positions=[1])                      # plain transpose + append
+    np.testing.assert_array_equal(out[0, :, 1:3], x[0].transpose(1, 0, 2))
+    assert (out[0, :, 0] == 0).all() and (out[0, :, 3] == 0).all()
+    w = np.ones(64, np.float32)
+    out2 = np.zeros((1, 2, 2, 64), np.float32)
+    c_oracle.qk_prologue(x, out2, weight=w)                          # unit RMS per head vector
+    np.testing.assert_allclose((out2 ** 2).mean(-1), 1.0, rtol=1e-4)
+    cos = np.zeros((2, 32), np.float32)
+    sin = np.ones((2, 32), np.float32)                               # quarter turn: [x1,x2] -> [-x2,x1]
+    out3 = np.zeros((1, 2, 2, 64), np.float32)
+    c_oracle.qk_prologue(x, out3, cos=cos, sin=sin)
+    xt = x[0].transpose(1, 0, 2)
+    np.testing.assert_allclose(out3[0, :, :, :32], -xt[:, :, 32:], rtol=1e-6)
+    np.testing.assert_allclose(out3[0, :, :, 32:], xt[:, :, :32], rtol=1e-6)

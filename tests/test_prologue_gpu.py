@@ -1,0 +1,100 @@
+"""Fused RMSNorm + rotary + layout + KV-append kernel against the oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from tyr_b200 import nn as tnn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# one bf16 rounding of an fp32 result: half an ulp relative, plus the fp32 arithmetic itself
+BF16_REL = 2.0 ** -8
+
+
+def rope_tables(max_pos, d, base=10000.0):
+    inv = 1.0 / (base ** (torch.arange(0, d // 2).float() / (d // 2)))
+    ang = torch.arange(max_pos).float()[:, None] * inv[None]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+def close(got, ref):
+    got = got.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert (np.abs(got - ref) <= BF16_REL * np.abs(ref) + 1e-6).all(), float(np.abs(got - ref).max())
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("use_norm,use_rope", [(True, True), (True, False), (False, True), (False, False)])
+def test_against_oracle(D, use_norm, use_rope):
+    g = torch.Generator(device="cpu").manual_seed(D)
+    B, S, H, cap = 3, 7, 4, 32
+    x = torch.randn(B, S, H, D, generator=g).bfloat16()
+    w = (torch.rand(D, generator=g) + 0.5) if use_norm else None
+    cos, sin = rope_tables(cap, D) if use_rope else (None, None)
+    pos = torch.tensor([0, 5, 25], dtype=torch.int32)
+    cache = torch.randn(B, H, cap, D, generator=g).bfloat16()
+    ref = cache.float().numpy().copy()
+    c_oracle.qk_prologue(x.float().numpy(), ref, None if w is None else w.numpy(),
+                         None if cos is None else cos.numpy(), None if sin is None else sin.numpy(),
+                         positions=pos.numpy())
+    out = cache.to(DEV)
+    tnn.qkPrologue(x.to(DEV), out, None if w is None else w.to(DEV), None if cos is None else cos.to(DEV),
+                   None if sin is None else sin.to(DEV), positions=pos.to(DEV))
+    close(out, ref)
+    # untouched rows of the cache are bit-identical
+    mask = torch.ones(B, cap, dtype=torch.bool)
+    for b, p0 in enumerate(pos.tolist()):
+        mask[b, p0:p0 + S] = False
+    assert torch.equal(out.cpu().transpose(1, 2)[mask], cache.transpose(1, 2)[mask])
+
+
+def test_golden_reference_chain():
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_prologue.npz"))
+    start = int(g["start"])
+    out = torch.tensor(g["cache"]).bfloat16().to(DEV)
+    tnn.qkPrologue(torch.tensor(g["x"]).bfloat16().to(DEV), out, torch.tensor(g["w"]).to(DEV),
+                   torch.tensor(g["cos"]).to(DEV), torch.tensor(g["sin"]).to(DEV), position0=start)
+    S = g["x"].shape[1]
+    close(out[:, :, start:start + S], g["new_cache"][:, :, start:start + S])
+
+
+def test_decode_step_through_prologue_and_flash_decode():
+    """One token of QwenAttention.forwardStep after the projections
+    (Tyr/Model/Qwen/Attention.lean:151-200): head norm, rotary, cache append, attention."""
+    g = torch.Generator(device="cpu").manual_seed(3)
+    B, Hq, Hkv, D, cap, seq = 2, 8, 2, 128, 300, 257
+    kc = torch.randn(B, Hkv, cap, D, generator=g).bfloat16()
+    vc = torch.randn(B, Hkv, cap, D, generator=g).bfloat16()
+    kc[:, :, seq:] = float("nan")
+    vc[:, :, seq:] = float("nan")
+    q = torch.randn(B, 1, Hq, D, generator=g).bfloat16()
+    k = torch.randn(B, 1, Hkv, D, generator=g).bfloat16()
+    v = torch.randn(B, 1, Hkv, D, generator=g).bfloat16()
+    qn, kn = torch.rand(D, generator=g) + 0.5, torch.rand(D, generator=g) + 0.5
+    cos, sin = rope_tables(cap, D)
+    # oracle: the same steps on fp32
+    kref, vref = kc.float().numpy().copy(), vc.float().numpy().copy()
+    c_oracle.qk_prologue(k.float().numpy(), kref, kn.numpy(), cos.numpy(), sin.numpy(), position0=seq)
+    c_oracle.qk_prologue(v.float().numpy(), vref, position0=seq)
+    qref = np.zeros((B, Hq, 1, D), np.float32)
+    c_oracle.qk_prologue(q.float().numpy(), qref, qn.numpy(), cos.numpy()[seq:], sin.numpy()[seq:])
+    bf = lambda a: torch.tensor(a).bfloat16().float().numpy()          # tensors are bf16 between ops
+    oref, _ = c_oracle.sdpa(bf(qref), bf(kref[:, :, :seq + 1]), bf(vref[:, :, :seq + 1]), False)
+    # device: three prologue launches and one decode launch, cache updated in place
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    tnn.qkPrologue(k.to(DEV), kd, kn.to(DEV), cos.to(DEV), sin.to(DEV), position0=seq)
+    tnn.qkPrologue(v.to(DEV), vd, position0=seq)
+    qd = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    tnn.qkPrologue(q.to(DEV), qd, qn.to(DEV), cos[seq:].contiguous().to(DEV), sin[seq:].contiguous().to(DEV))
+    o, _ = tnn.flashDecodeDense(qd, kd, vd, kv_len=seq + 1)
+    assert np.abs(o.float().cpu().numpy() - oref[:, :, 0]).max() <= 2e-2
+
+
+def test_rejects_bad_arguments():
+    from tyr_b200 import _lib
+    x = torch.zeros(1, 1, 1, 96, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(1, 1, 4, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(_lib.AttnError):
+        tnn.qkPrologue(x, out)

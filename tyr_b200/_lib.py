@@ -21,7 +21,7 @@ DECODE_STATIC_SCRATCH_BYTES = 16 << 20   # TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES
 EXPORTS = [
     "tyr_b200_attn_prefill", "tyr_b200_sdpa_4d", "tyr_b200_sdpa_gqa", "tyr_b200_sdpa_gqa_qkv",
     "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_decode_static",
-    "tyr_b200_attn_merge",
+    "tyr_b200_attn_merge", "tyr_b200_attn_qk_prologue",
     "tyr_b200_attn_prefill_host", "tyr_b200_attn_device_status", "tyr_b200_attn_strerror",
     "tyr_b200_attn_abi_version", "tyr_b200_attn_launch_count",
 ]
@@ -47,6 +47,14 @@ class DecodeArgs(ctypes.Structure):
         ("q_stride", c_i64 * 2), ("o_stride", c_i64 * 2), ("k_stride", c_i64 * 3),
         ("v_stride", c_i64 * 3),
         ("scale", c_f32), ("max_splits", c_i32), ("workspace", vp), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+class PrologueArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", vp), ("out", vp), ("norm_weight", vp), ("cos", vp), ("sin", vp), ("positions", vp),
+        ("position0", c_i32), ("batch", c_i32), ("seq", c_i32), ("n_head", c_i32), ("head_dim", c_i32),
+        ("x_stride", c_i64 * 3), ("out_stride", c_i64 * 3), ("eps", c_f32),
     ]
 
 
@@ -79,6 +87,8 @@ def load() -> ctypes.CDLL:
     L.tyr_b200_attn_decode.restype = ctypes.c_int
     L.tyr_b200_attn_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), vp]
     L.tyr_b200_attn_decode_static.restype = ctypes.c_int
+    L.tyr_b200_attn_qk_prologue.argtypes = [ctypes.POINTER(PrologueArgs), vp]
+    L.tyr_b200_attn_qk_prologue.restype = ctypes.c_int
     L.tyr_b200_attn_merge.argtypes = [vp] * 6 + [c_i64, c_i32, vp]
     L.tyr_b200_attn_merge.restype = ctypes.c_int
     L.tyr_b200_attn_device_status.argtypes = [c_i32, c_i32]

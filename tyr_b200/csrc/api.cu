@@ -21,10 +21,13 @@ std::mutex g_host_mu;  // serialises the host-buffer call and guards g_stage
 DeviceState g_state[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
 
+constexpr int kMaxHostChunks = 64;
 struct HostStage {  // device staging buffers of the host-buffer call, grown on demand
   void* buf = nullptr;
   size_t bytes = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;      // host->device copies and the kernels
+  cudaStream_t out_stream = nullptr;  // device->host copies (the other copy engine)
+  cudaEvent_t done[kMaxHostChunks] = {};  // kernel of chunk i finished
 };
 HostStage g_stage[kMaxDevices];
 
@@ -193,6 +196,18 @@ int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, 
                        static_cast<cudaStream_t>(stream));
 }
 
+int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* a, void* stream) {
+  if (!a || !a->x || !a->out) return -TYR_ATTN_ERR_NULL;
+  if ((a->cos == nullptr) != (a->sin == nullptr)) return -TYR_ATTN_ERR_NULL;
+  if (a->batch <= 0 || a->seq <= 0 || a->n_head <= 0 || a->position0 < 0) return -TYR_ATTN_ERR_SHAPE;
+  if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return -TYR_ATTN_ERR_HEAD_DIM;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 3u) || (reinterpret_cast<uintptr_t>(a->out) & 3u))
+    return -TYR_ATTN_ERR_ALIGN;
+  for (int i = 0; i < 3; ++i)
+    if ((a->x_stride[i] & 1) || (a->out_stride[i] & 1)) return -TYR_ATTN_ERR_ALIGN;
+  return launch_qk_prologue(*a, static_cast<cudaStream_t>(stream));
+}
+
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   int rc = check_prefill(a);
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment
@@ -229,19 +244,45 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   contiguous_strides(d.k_stride, a->n_kv_head, a->kv_seq, a->head_dim);
   contiguous_strides(d.v_stride, a->n_kv_head, a->kv_seq, a->head_dim);
   contiguous_strides(d.o_stride, a->n_head, a->q_seq, a->head_dim);
-  cudaStream_t st = hs.stream;
-  if ((e = cudaMemcpyAsync(base, a->q, nq * es, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-      (e = cudaMemcpyAsync(base + off_k, a->k, nk * es, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-      (e = cudaMemcpyAsync(base + off_v, a->v, nk * es, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+  if (!hs.out_stream &&
+      (e = cudaStreamCreateWithFlags(&hs.out_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail((int)e);
-  rc = tyr_b200_attn_prefill(&d, st);
-  if (rc) return fail(rc);
-  if ((e = cudaMemcpyAsync(a->o, base + off_o, nq * es, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
-    return fail((int)e);
-  if (a->lse &&
-      (e = cudaMemcpyAsync(a->lse, base + off_l, nl * 4, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
-    return fail((int)e);
-  e = cudaStreamSynchronize(st);
+  // Pipeline over the batch: while chunk i computes and chunk i-1 drains to the host on
+  // the device->host copy engine, chunk i+1 is already arriving on the host->device one.
+  const int n_chunks = a->batch < kMaxHostChunks ? a->batch : kMaxHostChunks;
+  cudaStream_t st = hs.stream, so = hs.out_stream;
+  const char *hq = static_cast<const char*>(a->q), *hk = static_cast<const char*>(a->k),
+             *hv = static_cast<const char*>(a->v);
+  char* ho = static_cast<char*>(a->o);
+  const size_t q1 = nq / a->batch * es, k1 = nk / a->batch * es, l1 = nl / a->batch * 4;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int b0 = (int)((long long)a->batch * c / n_chunks), b1 = (int)((long long)a->batch * (c + 1) / n_chunks);
+    const size_t nb = (size_t)(b1 - b0);
+    if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
+      return fail((int)e);
+    if ((e = cudaMemcpyAsync(base + b0 * q1, hq + b0 * q1, nb * q1, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(base + off_k + b0 * k1, hk + b0 * k1, nb * k1, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(base + off_v + b0 * k1, hv + b0 * k1, nb * k1, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+      return fail((int)e);
+    TyrAttnPrefillArgs dc = d;
+    dc.batch = (int32_t)nb;
+    dc.q = base + b0 * q1;
+    dc.k = base + off_k + b0 * k1;
+    dc.v = base + off_v + b0 * k1;
+    dc.o = base + off_o + b0 * q1;
+    dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + b0 * l1) : nullptr;
+    rc = tyr_b200_attn_prefill(&dc, st);
+    if (rc) return fail(rc);
+    if ((e = cudaEventRecord(hs.done[c], st)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(ho + b0 * q1, base + off_o + b0 * q1, nb * q1, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+      return fail((int)e);
+    if (a->lse && (e = cudaMemcpyAsync(reinterpret_cast<char*>(a->lse) + b0 * l1, base + off_l + b0 * l1,
+                                       nb * l1, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+      return fail((int)e);
+  }
+  e = cudaStreamSynchronize(so);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   return fail((int)e);
 }
 

@@ -26,4 +26,7 @@ int launch_decode(const TyrAttnDecodeArgs& a, float scale, cudaStream_t st);
 int launch_merge2(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
                   float* o_out, float* lse_out, int64_t rows, int head_dim, cudaStream_t st);
 
+// qk_prologue.cu
+int launch_qk_prologue(const TyrAttnPrologueArgs& a, cudaStream_t st);
+
 }  // namespace tyr

@@ -20,7 +20,7 @@ from typing import Optional, Sequence, Tuple
 import torch
 
 from . import _lib
-from ._lib import AttnError, DecodeArgs, PrefillArgs, check
+from ._lib import AttnError, DecodeArgs, PrefillArgs, PrologueArgs, check
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -281,6 +281,43 @@ def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     with torch.cuda.device(q.device):
         check(L.tyr_b200_attn_decode(ctypes.byref(a), _stream_ptr(q)))
     return out, lse
+
+
+def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+               cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+               positions: Optional[torch.Tensor] = None, position0: int = 0, eps: float = 1e-6):
+    """Fused per-head RMSNorm + rotary embedding + [B,S,H,D] -> [B,H,S,D] layout change,
+    written into `out` [B,H,cap,D] at rows positions[b] + s (in place: a KV-cache append
+    when `out` is the cache).  One pass instead of applyHeadNorm
+    (Tyr/Model/Qwen/Attention.lean:73-98), rotary.applyRotaryEmb (Tyr/Torch.lean:1043-1048),
+    transpose_for_attention (Tyr/Torch.lean:589-597) and data.sliceScatter
+    (Tyr/Model/Qwen/Attention.lean:189-193).  `norm_weight` [D] and `cos`/`sin`
+    [max_pos, D/2] are float32 device tensors; `positions` is int32 [B].
+    """
+    _require_cuda(x, out)
+    if x.dim() != 4 or out.dim() != 4 or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise ValueError("x must be bf16 [B,S,H,D] and out bf16 [B,H,cap,D]")
+    B, S, H, D = x.shape
+    if out.shape[0] != B or out.shape[1] != H or out.shape[3] != D:
+        raise ValueError("out does not match x")
+    for t_ in (norm_weight, cos, sin):
+        if t_ is not None and (t_.dtype != torch.float32 or not t_.is_contiguous() or not t_.is_cuda):
+            raise ValueError("norm_weight / cos / sin must be contiguous float32 CUDA tensors")
+    if positions is not None and (positions.dtype != torch.int32 or not positions.is_cuda):
+        raise ValueError("positions must be an int32 CUDA tensor")
+    a = PrologueArgs()
+    a.x, a.out = x.data_ptr(), out.data_ptr()
+    a.norm_weight = norm_weight.data_ptr() if norm_weight is not None else None
+    a.cos = cos.data_ptr() if cos is not None else None
+    a.sin = sin.data_ptr() if sin is not None else None
+    a.positions = positions.data_ptr() if positions is not None else None
+    a.position0, a.batch, a.seq, a.n_head, a.head_dim = int(position0), B, S, H, D
+    a.x_stride[:] = [x.stride(0), x.stride(1), x.stride(2)]
+    a.out_stride[:] = [out.stride(0), out.stride(1), out.stride(2)]
+    a.eps = float(eps)
+    with torch.cuda.device(x.device):
+        check(_lib.load().tyr_b200_attn_qk_prologue(ctypes.byref(a), _stream_ptr(x)))
+    return out
 
 
 def mergePartials(o_a, lse_a, o_b, lse_b):
