@@ -39,38 +39,42 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll of a phase.  The suspend-time hint lets the hardware park the warp until the
+// phase completes (or the hint, in nanoseconds, runs out) instead of spinning: a spinning
+// control warp would take issue slots from the softmax warps of its SM sub-partition.
+constexpr uint32_t kSuspendHintNs = 200000u;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok;
 }
 
-// Wait limit for any single mbarrier phase.  Far above any legitimate wait
-// (the longest is one KV tile of work, microseconds) and short enough that a
-// protocol error ends the kernel instead of holding the GPU.
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+// Wait limit for any single mbarrier phase, in SM clock cycles (2-4 s at 1-2 GHz).  Far
+// above any legitimate wait (the longest is one KV tile of work, microseconds) and
+// short enough that a protocol error ends the kernel instead of holding the GPU.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: non-zero means some role of
 // this CTA already gave up, so everyone else leaves too.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  for (uint32_t it = 0;; ++it) {
+  long long t0 = 0;
+#pragma unroll 1
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u) {
-      if (*abort_flag) return false;
-      uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
-        *abort_flag = kStatusWaitTimeout;
-        return false;
-      }
+    if (*abort_flag) return false;
+    const long long now = clock64();
+    if (t0 == 0) {
+      t0 = now;
+    } else if (now - t0 > kWaitLimitCycles) {
+      *abort_flag = kStatusWaitTimeout;
+      return false;
     }
   }
 }
