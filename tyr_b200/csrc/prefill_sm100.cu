@@ -389,6 +389,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, sr[c]);
         tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) tmem_ld_ready(sr[c]);
 
         // keys this row may see in this tile: [0, limit)
         int limit = p.kv_seq - j * kBN;
@@ -427,6 +429,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               uint32_t o[32];
               tmem_ld32(tO + c * 32, o);
               tmem_wait_ld();
+              tmem_ld_ready(o);
 #pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
               tmem_st32(tO + c * 32, o);
@@ -474,6 +477,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         uint32_t o[32];
         tmem_ld32(tO + c * 32, o);
         tmem_wait_ld();
+        tmem_ld_ready(o);
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint4 wv;
