@@ -34,7 +34,7 @@ UNIT = "TFLOP/s"
 DEFAULT_WORKLOAD = "qwen3_0p6b_prefill"
 # dram__bytes_read.sum + dram__bytes_write.sum of one prefill launch, from the ncu
 # capture summarised in profiles/prefill_kernel_qwen3_0p6b_prefill.md (None: no capture for that workload)
-NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": 177458944}
+NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": 208626176}
 
 
 def load_peaks():
@@ -134,17 +134,19 @@ def run_reference(args):
     if rank != 0:
         return 0
     w = W.WORKLOADS[args.workload]
+    # torchrun exports OMP_NUM_THREADS=1; the reference gets every host core it can use
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     flops, times = time_cpu(w, args.steps, args.warmup)
     sec = sum(times) / len(times)
     val = flops / sec / 1e12
     threads = torch.get_num_threads()
-    sample = (f"full {w.name} batch per step: ATen scaled_dot_product_attention on fp32 CPU tensors "
+    sample = (f"one GPU's {w.name} batch (B={w.batch}) per step: ATen scaled_dot_product_attention on fp32 CPU tensors "
               f"(bf16-rounded values), repeat_interleave GQA expansion inside the call, torch {torch.__version__}")
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(w, 1),
+        "config": workload_config(w, max(args.gpus, 1)),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -212,6 +214,21 @@ def other_workloads(tnn, dev, peaks, steps=10, warmup=3):
     out[w.name] = {"ms": sec * 1e3, "kv_gbs": byts / sec / 1e9, "kv_bytes": byts,
                    "frac_hbm_peak": byts / sec / 1e9 / peaks["hbm_gbs"],
                    "l2": "4.8 GB of KV per step, far above L2"}
+    # fused K prologue (RMSNorm + rotary + layout + append) on the decode workload's batch:
+    # 4096 new tokens per sequence appended to a dense cache; bytes = one read + one write
+    B, S, H, D, cap = 16, 4096, 8, 128, 8192
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(B, S, H, D, device=dev, generator=g).bfloat16()
+    cache = torch.zeros(B, H, cap, D, device=dev, dtype=torch.bfloat16)
+    wn = torch.ones(D, device=dev)
+    ang = torch.arange(cap, device=dev).float()[:, None] * (1.0 / (10000.0 ** (torch.arange(D // 2, device=dev).float() / (D // 2))))[None]
+    cs, sn = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.full((B,), 1024, dtype=torch.int32, device=dev)
+    sec = time_events(lambda: tnn.qkPrologue(x, cache, wn, cs, sn, positions=pos), steps, warmup, lambda: None) / steps
+    byts = 2 * x.numel() * 2
+    out["k_prologue_append"] = {"ms": sec * 1e3, "gbs": byts / sec / 1e9, "bytes": byts,
+                                "frac_hbm_peak": byts / sec / 1e9 / peaks["hbm_gbs"],
+                                "l2": "134 MB in + 134 MB out per step, above L2"}
     return out
 
 
@@ -314,6 +331,7 @@ def run_ours(args):
         cpu = None
         others = None
         if world == 1:
+            torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
             flops, times = time_cpu(w, 3, 1)
             best = min(times)
             cpu = {"value": flops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),

@@ -182,6 +182,7 @@ int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, 
  *   [y1, y2] -> [y1*cos - y2*sin, y1*sin + y2*cos]         (skipped when cos == NULL)
  *   out[b, h, pos_b + s, :] = bf16(y)      with pos_b = positions ? positions[b] : position0
  * cos/sin: fp32 [max_pos, head_dim/2] indexed by pos_b + s.  head_dim in {64,128,256}.
+ * x, out, norm_weight, cos, sin are 16-byte aligned; strides are multiples of 8 elements.
  * For Q pass position0 = rotary offset and an out tensor whose row 0 is that offset
  * (out pointer already shifted); for K/V pass the cache and the sequence lengths.
  * ---------------------------------------------------------------------- */

@@ -201,10 +201,11 @@ int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* a, void* stream) {
   if ((a->cos == nullptr) != (a->sin == nullptr)) return -TYR_ATTN_ERR_NULL;
   if (a->batch <= 0 || a->seq <= 0 || a->n_head <= 0 || a->position0 < 0) return -TYR_ATTN_ERR_SHAPE;
   if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return -TYR_ATTN_ERR_HEAD_DIM;
-  if ((reinterpret_cast<uintptr_t>(a->x) & 3u) || (reinterpret_cast<uintptr_t>(a->out) & 3u))
+  if (!aligned16(a->x) || !aligned16(a->out) || (a->norm_weight && !aligned16(a->norm_weight)) ||
+      (a->cos && (!aligned16(a->cos) || !aligned16(a->sin))))
     return -TYR_ATTN_ERR_ALIGN;
   for (int i = 0; i < 3; ++i)
-    if ((a->x_stride[i] & 1) || (a->out_stride[i] & 1)) return -TYR_ATTN_ERR_ALIGN;
+    if ((a->x_stride[i] & 7) || (a->out_stride[i] & 7)) return -TYR_ATTN_ERR_ALIGN;
   return launch_qk_prologue(*a, static_cast<cudaStream_t>(stream));
 }
 

@@ -29,76 +29,83 @@ struct PrologueParams {
   float eps;
 };
 
-// One warp per (batch, token, head) row.  Lane l owns elements {2l, 2l+1} (+64k) of each
-// half of the row, so a rotary pair (i, i + d/2) lives in one lane.
+// D/16 lanes per (batch, token, head) row: a lane owns elements [8k, 8k+8) of BOTH halves
+// of the row (two 16-byte loads), so every rotary pair (i, i + D/2) lives in one lane and
+// a warp covers 512/D rows per pass.
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32)
 prologue_kernel(const PrologueParams p) {
   constexpr int kHalf = D / 2;
-  constexpr int kPer = kHalf / 64 > 0 ? kHalf / 64 : 1;  // bf16x2 pairs per lane per half
-  constexpr bool kNarrow = kHalf < 64;                   // d = 64: one element per lane per half
+  constexpr int kLanes = D / 16;          // lanes per row
+  constexpr int kRowsPerWarp = 32 / kLanes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarps + warp;
+  const int sub = lane / kLanes, k8 = (lane % kLanes) * 8;
   const int64_t rows = (int64_t)p.batch * p.seq * p.n_head;
-  if (row >= rows) return;
-  const int h = (int)(row % p.n_head);
-  const int s = (int)((row / p.n_head) % p.seq);
-  const int b = (int)(row / ((int64_t)p.n_head * p.seq));
+  const int64_t row = ((int64_t)blockIdx.x * kWarps + warp) * kRowsPerWarp + sub;
+  const bool live = row < rows;
+  const int64_t rr = live ? row : rows - 1;  // idle lanes redo the last row and skip the store
+  const int h = (int)(rr % p.n_head);
+  const int s = (int)((rr / p.n_head) % p.seq);
+  const int b = (int)(rr / ((int64_t)p.n_head * p.seq));
   const int pos = (p.positions ? p.positions[b] : p.position0) + s;  // output row and rotary position
 
   const __nv_bfloat16* xr = p.x + b * p.xs[0] + s * p.xs[1] + h * p.xs[2];
   __nv_bfloat16* orow = p.out + b * p.os[0] + h * p.os[1] + (int64_t)pos * p.os[2];
 
-  float x1[2 * kPer], x2[2 * kPer];
-  float ss = 0.f;
-  if (kNarrow) {
-    x1[0] = __bfloat162float(xr[lane]);
-    x2[0] = __bfloat162float(xr[kHalf + lane]);
-    ss = x1[0] * x1[0] + x2[0] * x2[0];
-  } else {
+  const uint4 ra = *reinterpret_cast<const uint4*>(xr + k8);
+  const uint4 rc = *reinterpret_cast<const uint4*>(xr + kHalf + k8);
+  float a[8], c[8];
+  {
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+    const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&rc);
 #pragma unroll
-    for (int k = 0; k < kPer; ++k) {
-      const int i = 64 * k + 2 * lane;
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + i));
-      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + kHalf + i));
-      x1[2 * k] = a.x; x1[2 * k + 1] = a.y; x2[2 * k] = c.x; x2[2 * k + 1] = c.y;
-      ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+    for (int i = 0; i < 4; ++i) {
+      const float2 fa = __bfloat1622float2(pa[i]), fc = __bfloat1622float2(pc[i]);
+      a[2 * i] = fa.x; a[2 * i + 1] = fa.y; c[2 * i] = fc.x; c[2 * i + 1] = fc.y;
     }
   }
-  float inv = 1.f;
   if (p.w != nullptr) {
+    float ss = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    inv = rsqrtf(ss / (float)D + p.eps);
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + c[i] * c[i];
+#pragma unroll
+    for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+    const float4 w0 = *reinterpret_cast<const float4*>(p.w + k8), w1 = *reinterpret_cast<const float4*>(p.w + k8 + 4);
+    const float4 w2 = *reinterpret_cast<const float4*>(p.w + kHalf + k8), w3 = *reinterpret_cast<const float4*>(p.w + kHalf + k8 + 4);
+    const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const float wc[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] *= inv * wa[i];
+      c[i] *= inv * wc[i];
+    }
   }
-  constexpr int kN = kNarrow ? 1 : 2 * kPer;
+  if (p.cs != nullptr) {
+    const float* cp = p.cs + (int64_t)pos * kHalf + k8;
+    const float* sp = p.sn + (int64_t)pos * kHalf + k8;
+    const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+    const float co[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float si[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-  for (int e = 0; e < kN; ++e) {
-    const int i = kNarrow ? lane : 64 * (e >> 1) + 2 * lane + (e & 1);
-    float a = x1[e], c = x2[e];
-    if (p.w != nullptr) {
-      a *= inv * p.w[i];
-      c *= inv * p.w[kHalf + i];
+    for (int i = 0; i < 8; ++i) {
+      const float y1 = a[i] * co[i] - c[i] * si[i], y2 = a[i] * si[i] + c[i] * co[i];
+      a[i] = y1;
+      c[i] = y2;
     }
-    if (p.cs != nullptr) {
-      const float co = p.cs[(int64_t)pos * kHalf + i], si = p.sn[(int64_t)pos * kHalf + i];
-      const float y1 = a * co - c * si, y2 = a * si + c * co;
-      a = y1;
-      c = y2;
-    }
-    x1[e] = a;
-    x2[e] = c;
   }
-  if (kNarrow) {
-    orow[lane] = __float2bfloat16_rn(x1[0]);
-    orow[kHalf + lane] = __float2bfloat16_rn(x2[0]);
-  } else {
+  if (live) {
+    uint4 oa, oc;
+    __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* qc = reinterpret_cast<__nv_bfloat162*>(&oc);
 #pragma unroll
-    for (int k = 0; k < kPer; ++k) {
-      const int i = 64 * k + 2 * lane;
-      *reinterpret_cast<__nv_bfloat162*>(orow + i) = __floats2bfloat162_rn(x1[2 * k], x1[2 * k + 1]);
-      *reinterpret_cast<__nv_bfloat162*>(orow + kHalf + i) = __floats2bfloat162_rn(x2[2 * k], x2[2 * k + 1]);
+    for (int i = 0; i < 4; ++i) {
+      qa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+      qc[i] = __floats2bfloat162_rn(c[2 * i], c[2 * i + 1]);
     }
+    *reinterpret_cast<uint4*>(orow + k8) = oa;
+    *reinterpret_cast<uint4*>(orow + kHalf + k8) = oc;
   }
 }
 
@@ -117,7 +124,8 @@ int launch_qk_prologue(const TyrAttnPrologueArgs& a, cudaStream_t st) {
   for (int i = 0; i < 3; ++i) { p.xs[i] = a.x_stride[i]; p.os[i] = a.out_stride[i]; }
   p.eps = a.eps;
   const int64_t rows = (int64_t)a.batch * a.seq * a.n_head;
-  const int64_t blocks = (rows + kWarps - 1) / kWarps;
+  const int rows_per_block = kWarps * (512 / a.head_dim);
+  const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   if (a.head_dim == 128) prologue_kernel<128><<<(unsigned)blocks, kWarps * 32, 0, st>>>(p);
   else if (a.head_dim == 64) prologue_kernel<64><<<(unsigned)blocks, kWarps * 32, 0, st>>>(p);
