@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 1
+#define TYR_ATTN_ABI_VERSION 2
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -71,6 +71,9 @@ typedef struct TyrAttnPrefillArgs {
   int32_t is_causal;  /* 0 | 1 */
   float scale;        /* 0 => 1/sqrt(head_dim), ATen's default */
   int32_t check_mode; /* 1 => fp32-FMA kernel (no tensor cores), any head_dim <= 256 */
+  int32_t window_size; /* 0 => none; w > 0 => key j is visible to query i only if j <= i and
+                          i - j < w (implies is_causal), the mask lean_torch_sdpa_gqa_window
+                          builds at cc/src/tyr.cpp:3986-3996 */
 } TyrAttnPrefillArgs;
 
 int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* args, void* stream);
@@ -93,6 +96,14 @@ int tyr_b200_sdpa_gqa_qkv(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, u
                           uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k,
                           const void* v, void* out, double dropout_p, uint8_t is_causal,
                           uint8_t enable_gqa, void* stream);
+/* tyr_b200_sdpa_gqa_window <- lean_torch_sdpa_gqa_window cc/src/tyr.cpp:3953-4018: causal
+ * sliding window, each query sees the last `window_size` keys including its own.  The
+ * reference ignores is_causal here (its mask is always causal | window); so does this call.
+ * No [seq, seq] mask tensor is built: tiles before the window are skipped. */
+int tyr_b200_sdpa_gqa_window(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                             uint64_t head_dim, const void* q, const void* k, const void* v,
+                             void* out, double dropout_p, uint8_t is_causal, uint8_t enable_gqa,
+                             uint64_t window_size, void* stream);
 
 /* ------------------------------------------------------------------------
  * Decode: one query token per sequence over a (possibly ragged) KV cache,

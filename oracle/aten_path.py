@@ -29,6 +29,24 @@ def sdpa_gqa(q, k, v, dropout_p: float = 0.0, is_causal: bool = True, enable_gqa
 sdpa_gqa_qkv = sdpa_gqa
 
 
+def sdpa_gqa_window(q, k, v, dropout_p: float = 0.0, is_causal: bool = True, enable_gqa: bool = True,
+                    window_size: int = 1):
+    """cc/src/tyr.cpp:3953-4018 (lean_torch_sdpa_gqa_window): explicit -inf/0 mask that hides
+    future keys and keys `window_size` or more positions back, then SDPA with is_causal=false."""
+    n_head, n_kv_head = q.shape[1], k.shape[1]
+    if enable_gqa and n_head != n_kv_head and n_kv_head > 0:
+        rep = n_head // n_kv_head
+        k = k.repeat_interleave(rep, 1)
+        v = v.repeat_interleave(rep, 1)
+    seq = q.shape[2]
+    row = torch.arange(seq).unsqueeze(1)
+    col = torch.arange(seq).unsqueeze(0)
+    combined = (col > row) | ((row - col) >= int(window_size))
+    mask = torch.where(combined, torch.full((seq, seq), float("-inf"), dtype=q.dtype),
+                       torch.zeros((seq, seq), dtype=q.dtype)).unsqueeze(0).unsqueeze(0)
+    return F.scaled_dot_product_attention(q, k, v, mask, dropout_p, False)
+
+
 def lse(q, k, v, is_causal: bool):
     """Natural-log LSE of the scaled scores, [B,Hq,Sq] fp32, from ATen's CPU flash kernel."""
     n_head, n_kv_head = q.shape[1], k.shape[1]

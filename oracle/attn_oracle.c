@@ -18,6 +18,8 @@
  *                          GQA head map of repeat_interleave (cc/src/tyr.cpp:3931-3938);
  *                          causal mask "col > row is masked" (cc/src/tyr.cpp:3990-3991);
  *                          LSE = log(sum(exp(scaled scores))) (RunFlashAttn.lean:45-48).
+ *   tyr_oracle_sdpa_window the same with the causal sliding-window mask of
+ *                          lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3953-4018).
  *   tyr_oracle_sdpa_online the running max / running sum form of
  *                          Tyr/GPU/Codegen/Macros.lean:121-163 with fp32 state.
  *   tyr_oracle_merge2      LSE merge of two partial results,
@@ -67,9 +69,12 @@ void tyr_oracle_bf16_round(const float* in, float* out, int64_t n) {
   }
 }
 
-/* Direct form.  Returns 0, or -1 on bad arguments. */
-int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, float* lse, int B,
-                    int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale) {
+/* Direct form.  Returns 0, or -1 on bad arguments.  window > 0 adds the sliding-window mask of
+ * lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3986-3996): key j is also hidden from query i
+ * when i - j >= window; that entry point always combines it with the causal mask. */
+static int sdpa_direct(const float* q, const float* k, const float* v, float* o, float* lse, int B,
+                       int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale,
+                       int window) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0) return -1;
   const int g = Hq / Hkv; /* query head h reads KV head h / g */
   const int64_t rows = (int64_t)B * Hq * Sq;
@@ -91,8 +96,9 @@ int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, fl
         const float* kb = k + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
         const float* vb = v + ((int64_t)b * Hkv + h / g) * (int64_t)Skv * D;
         const int n = is_causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv; /* keys j <= i */
+        const int j0 = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0; /* i - j < window */
         double mx = -INFINITY;
-        for (int j = 0; j < n; ++j) {
+        for (int j = j0; j < n; ++j) {
           const float* kr = kb + (int64_t)j * D;
           double dot = 0.0;
           for (int d = 0; d < D; ++d) dot += (double)qr[d] * (double)kr[d];
@@ -101,7 +107,7 @@ int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, fl
         }
         double sum = 0.0;
         for (int d = 0; d < D; ++d) acc[d] = 0.0;
-        for (int j = 0; j < n; ++j) {
+        for (int j = j0; j < n; ++j) {
           const double p = exp(s[j] - mx);
           sum += p;
           const float* vr = vb + (int64_t)j * D;
@@ -115,6 +121,17 @@ int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, fl
     free(acc);
   }
   return failed ? -1 : 0;
+}
+
+int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, float* lse, int B,
+                    int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale) {
+  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, Sq, Skv, D, is_causal, scale, 0);
+}
+
+int tyr_oracle_sdpa_window(const float* q, const float* k, const float* v, float* o, float* lse,
+                           int B, int Hq, int Hkv, int S, int D, float scale, int window) {
+  if (window <= 0) return -1;
+  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, S, S, D, 1, scale, window);
 }
 
 /* Online form with fp32 state, keys visited in blocks of `block` (Macros.lean:121-163):

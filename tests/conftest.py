@@ -26,6 +26,8 @@ def golden():
     out = {}
     for n in names:
         case = {f: data[f"{n}.{f}"] for f in ("o", "lse", "meta")}
+        if case["meta"].size < 8:      # [B, Hq, Hkv, Sq, Skv, D, causal, window]
+            case["meta"] = np.append(case["meta"], 0)
         for f in ("q", "k", "v"):  # stored as bf16 bit patterns
             case[f] = (data[f"{n}.{f}"].astype(np.uint32) << 16).view(np.float32)
         out[n] = case

@@ -23,7 +23,11 @@ CASES = {
     "decode_gqa_step": ("sdpa_gqa_qkv", 2, 4, 1, 1, 77, 128, False, False),
     "qkv_causal_topleft": ("sdpa_gqa_qkv", 1, 2, 1, 5, 9, 64, True, False),
     "tile_edge_129": ("sdpa_gqa", 1, 2, 1, 129, 129, 64, True, False),
+    # sliding window (lean_torch_sdpa_gqa_window); the window size rides in WINDOWS below
+    "window_7": ("sdpa_gqa_window", 1, 2, 1, 50, 50, 64, True, False),
+    "window_140": ("sdpa_gqa_window", 1, 1, 1, 260, 260, 64, True, True),
 }
+WINDOWS = {"window_7": 7, "window_140": 140}
 
 
 def rms(x):
@@ -40,17 +44,21 @@ def main():
         if norm:
             q, k = rms(q), rms(k)
         q, k, v = (t.bfloat16().float() for t in (q, k, v))
+        win = WINDOWS.get(name, 0)
         if fn == "sdpa_4d":
             o = aten_path.sdpa_4d(q, k, v, 0.0, causal)
+        elif win:
+            o = aten_path.sdpa_gqa_window(q, k, v, 0.0, causal, True, win)
         else:
             o = getattr(aten_path, fn)(q, k, v, 0.0, causal, True)
-        lse = aten_path.lse(q, k, v, causal)
+        # ATen returns no LSE for a masked call: windowed cases store zeros and pin O only
+        lse = aten_path.lse(q, k, v, causal) if not win else torch.zeros(B, Hq, Sq)
         # inputs are bf16-representable: store the upper 16 bits only
         for key, t in (("q", q), ("k", k), ("v", v)):
             out[f"{name}.{key}"] = (t.numpy().view(np.uint32) >> 16).astype(np.uint16)
         for key, t in (("o", o), ("lse", lse)):
             out[f"{name}.{key}"] = t.numpy()
-        out[f"{name}.meta"] = np.array([B, Hq, Hkv, Sq, Skv, D, int(causal)])
+        out[f"{name}.meta"] = np.array([B, Hq, Hkv, Sq, Skv, D, int(causal), win])
     path = os.path.join(os.path.dirname(__file__), "aten_sdpa.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")

@@ -13,10 +13,11 @@ def rel(a, b):
 def test_oracle_matches_golden_aten_outputs(golden):
     assert len(golden) >= 6
     for name, g in golden.items():
-        causal = bool(g["meta"][6])
-        o, lse = c_oracle.sdpa(g["q"], g["k"], g["v"], causal)
+        causal, win = bool(g["meta"][6]), int(g["meta"][7])
+        o, lse = c_oracle.sdpa(g["q"], g["k"], g["v"], causal, window=win)
         assert rel(o, g["o"]) < 1e-5, name
-        assert rel(lse, g["lse"]) < 1e-5, name
+        if not win:      # ATen returns no LSE for the masked (windowed) call
+            assert rel(lse, g["lse"]) < 1e-5, name
 
 
 def test_golden_still_matches_this_torch(golden):
@@ -28,6 +29,8 @@ def test_golden_still_matches_this_torch(golden):
 
 def test_online_form_equals_direct_form(golden):
     for name, g in golden.items():
+        if int(g["meta"][7]):
+            continue
         causal = bool(g["meta"][6])
         o, lse = c_oracle.sdpa(g["q"], g["k"], g["v"], causal)
         for block in (1, 7, 64):
@@ -145,3 +148,21 @@ def test_prologue_oracle_parts():
     xt = x[0].transpose(1, 0, 2)
     np.testing.assert_allclose(out3[0, :, :, :32], -xt[:, :, 32:], rtol=1e-6)
     np.testing.assert_allclose(out3[0, :, :, 32:], xt[:, :, :32], rtol=1e-6)
+
+
+def test_window_closed_forms():
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((1, 2, 40, 32), dtype=np.float32)
+    k = rng.standard_normal((1, 2, 40, 32), dtype=np.float32)
+    v = rng.standard_normal((1, 2, 40, 32), dtype=np.float32)
+    o, lse = c_oracle.sdpa(q, k, v, True, window=1)          # each query sees only its own key
+    np.testing.assert_allclose(o, v, rtol=1e-6)
+    np.testing.assert_allclose(lse, (q * k).sum(-1) / np.sqrt(32.0), rtol=1e-5, atol=1e-6)
+    o_full, lse_full = c_oracle.sdpa(q, k, v, True)
+    o_w, lse_w = c_oracle.sdpa(q, k, v, True, window=40)     # window >= seq is plain causal
+    np.testing.assert_array_equal(o_w, o_full)
+    np.testing.assert_array_equal(lse_w, lse_full)
+    o5, _ = c_oracle.sdpa(q, k, v, True, window=5)           # row i == causal attention on keys i-4..i
+    i = 20
+    oi, _ = c_oracle.sdpa(q[:, :, i:i + 1], k[:, :, i - 4:i + 1], v[:, :, i - 4:i + 1], False)
+    np.testing.assert_allclose(o5[:, :, i:i + 1], oi, rtol=1e-5, atol=1e-6)

@@ -42,17 +42,30 @@ def _status_clean():
 
 def test_golden_vectors(golden):
     for name, g in golden.items():
-        causal = bool(g["meta"][6])
-        D = int(g["meta"][5])
+        causal, win = bool(g["meta"][6]), int(g["meta"][7])
         q, k, v = (torch.tensor(g[x]).bfloat16().to(DEV) for x in ("q", "k", "v"))
-        o, lse = tnn.attentionFwd(q, k, v, is_causal=causal)
-        assert_parity(o, lse, g["o"], g["lse"], name)
+        o, lse = tnn.attentionFwd(q, k, v, is_causal=causal, window_size=win)
+        assert_parity(o, None if win else lse, g["o"], g["lse"], name)
         # check mode on the same (bf16-exact) fp32 inputs
         qf, kf, vf = (torch.tensor(g[x]).to(DEV) for x in ("q", "k", "v"))
-        o32, lse32 = tnn.attentionFwd(qf, kf, vf, is_causal=causal, check_mode=True)
+        o32, lse32 = tnn.attentionFwd(qf, kf, vf, is_causal=causal, check_mode=True, window_size=win)
         scale = np.abs(g["o"]).max()
         assert np.abs(o32.cpu().numpy() - g["o"]).max() / scale <= CHECK_REL, name
-        assert (np.abs(lse32.cpu().numpy() - g["lse"]) / np.maximum(np.abs(g["lse"]), 1.0)).max() <= CHECK_REL, name
+        if not win:
+            assert (np.abs(lse32.cpu().numpy() - g["lse"]) / np.maximum(np.abs(g["lse"]), 1.0)).max() <= CHECK_REL, name
+
+
+@pytest.mark.parametrize("S", [200, 257, 700, 1300])
+@pytest.mark.parametrize("window", [1, 7, 64, 128, 129, 300, 5000])
+@pytest.mark.parametrize("D", [64, 128])
+def test_sliding_window(S, window, D):
+    # lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3953-4018): j <= i and i - j < window
+    q, k, v = randn(1, 4, S, D, seed=S + window), randn(1, 2, S, D, seed=S + 1), randn(1, 2, S, D, seed=S + 2)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, window_size=window)
+    ro, rlse = c_oracle.sdpa(q.float().numpy(), k.float().numpy(), v.float().numpy(), True, window=window)
+    assert_parity(o, lse, ro, rlse, (S, window, D))
+    o2 = tnn.scaledDotProductAttentionGQAWindow(q.to(DEV), k.to(DEV), v.to(DEV), 0.0, False, True, window)
+    assert torch.equal(o2, o)       # the typed call ignores is_causal, like the reference
 
 
 @pytest.mark.parametrize("S", [1, 63, 64, 65, 127, 128, 129, 255, 256, 257, 383, 512, 700])

@@ -5,6 +5,7 @@
 // raw-pointer terms: non-null, sizes, alignment, dtype.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstring>
@@ -51,6 +52,7 @@ int check_prefill(const TyrAttnPrefillArgs* a) {
   if (a->dtype != TYR_ATTN_BF16 && a->dtype != TYR_ATTN_F32) return -TYR_ATTN_ERR_DTYPE;
   if (a->dtype == TYR_ATTN_F32 && !a->check_mode) return -TYR_ATTN_ERR_DTYPE;
   if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
+  if (a->window_size < 0) return -TYR_ATTN_ERR_SHAPE;
   if (!a->check_mode) {
     if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
@@ -77,7 +79,8 @@ void contiguous_strides(int64_t* s, int64_t heads, int64_t seq, int64_t d) {
 
 int sdpa_contiguous(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t q_seq,
                     uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k, const void* v,
-                    void* out, double dropout_p, uint8_t is_causal, void* stream) {
+                    void* out, double dropout_p, uint8_t is_causal, void* stream,
+                    uint64_t window_size = 0) {
   if (dropout_p != 0.0) return -TYR_ATTN_ERR_DROPOUT;
   if (batch > 0x7fffffffu || n_head > 0x7fffffffu || n_kv_head > 0x7fffffffu ||
       q_seq > 0x7fffffffu || kv_seq > 0x7fffffffu || head_dim > 0x7fffffffu)
@@ -93,6 +96,7 @@ int sdpa_contiguous(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_
   contiguous_strides(a.o_stride, a.n_head, a.q_seq, a.head_dim);
   a.dtype = TYR_ATTN_BF16;
   a.is_causal = is_causal ? 1 : 0;
+  a.window_size = (int32_t)std::min<uint64_t>(window_size, 0x7fffffffu);
   return tyr_b200_attn_prefill(&a, stream);
 }
 
@@ -158,6 +162,16 @@ int tyr_b200_sdpa_gqa_qkv(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, u
   if (!enable_gqa && n_head != n_kv_head) return -TYR_ATTN_ERR_SHAPE;
   return sdpa_contiguous(batch, n_head, n_kv_head, q_seq, kv_seq, head_dim, q, k, v, out, dropout_p,
                          is_causal, stream);
+}
+
+int tyr_b200_sdpa_gqa_window(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                             uint64_t head_dim, const void* q, const void* k, const void* v,
+                             void* out, double dropout_p, uint8_t /*is_causal*/, uint8_t enable_gqa,
+                             uint64_t window_size, void* stream) {
+  if (!enable_gqa && n_head != n_kv_head) return -TYR_ATTN_ERR_SHAPE;
+  if (window_size == 0) return -TYR_ATTN_ERR_SHAPE;  // the reference's mask would hide every key
+  return sdpa_contiguous(batch, n_head, n_kv_head, seq, seq, head_dim, q, k, v, out, dropout_p, 1,
+                         stream, window_size);
 }
 
 size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim,

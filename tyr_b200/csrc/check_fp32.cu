@@ -24,7 +24,7 @@ struct CheckParams {
   const void *q, *k, *v;
   void* o;
   float* lse;
-  int batch, n_head, n_kv_head, q_seq, kv_seq, d, causal;
+  int batch, n_head, n_kv_head, q_seq, kv_seq, d, causal, window;
   int64_t qs[3], ks[3], vs[3], os[3];
   float scale;
 };
@@ -50,12 +50,13 @@ check_kernel(const CheckParams p) {
   __syncwarp();
 
   const int n_keys = p.causal ? min(p.kv_seq, i + 1) : p.kv_seq;  // key j masked when j > i
+  const int key_lo = p.window > 0 ? max(0, i - p.window + 1) : 0;  // and when i - j >= window
   float m = -INFINITY, l = 0.f;
   float acc[kMaxD / 32];
 #pragma unroll
   for (int x = 0; x < kMaxD / 32; ++x) acc[x] = 0.f;
 
-  for (int k0 = 0; k0 < n_keys; k0 += 32) {
+  for (int k0 = key_lo; k0 < n_keys; k0 += 32) {
     const int key = k0 + lane;
     float s = -INFINITY;
     if (key < n_keys) {
@@ -111,7 +112,9 @@ int launch_prefill_check(const TyrAttnPrefillArgs& a, float scale, cudaStream_t 
   CheckParams p;
   p.q = a.q; p.k = a.k; p.v = a.v; p.o = a.o; p.lse = a.lse;
   p.batch = a.batch; p.n_head = a.n_head; p.n_kv_head = a.n_kv_head;
-  p.q_seq = a.q_seq; p.kv_seq = a.kv_seq; p.d = a.head_dim; p.causal = a.is_causal;
+  p.q_seq = a.q_seq; p.kv_seq = a.kv_seq; p.d = a.head_dim;
+  p.causal = (a.is_causal || a.window_size > 0) ? 1 : 0;
+  p.window = a.window_size > 0 ? a.window_size : 0;
   for (int i = 0; i < 3; ++i) {
     p.qs[i] = a.q_stride[i]; p.ks[i] = a.k_stride[i]; p.vs[i] = a.v_stride[i]; p.os[i] = a.o_stride[i];
   }

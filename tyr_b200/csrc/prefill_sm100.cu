@@ -49,6 +49,7 @@ struct PrefillParams {
   float* lse;
   int64_t lse_stride_b, lse_stride_h;
   int q_seq, kv_seq, group, causal;
+  int window;  // 0: none; > 0: key j visible to query i only while i - j < window (causal)
   int n_head, batch, n_mblk;  // work items: n_mblk x n_head x batch
   int n_kv_head, groups_per_chunk;  // (batch, KV head) groups whose K/V share L2 at one time
   int snake;  // 1: odd rounds of the static schedule are mirrored
@@ -100,8 +101,11 @@ struct Bars {
 // balanced and the light items fill the tail), and the query heads that share a KV
 // head are neighbours, so CTAs running at the same time read the same K/V tiles.
 struct Item {
-  int mblk, hq, b, hkv, row0, n0, n1;
+  int mblk, hq, b, hkv, row0;
+  int lo;      // first KV tile of the item (> 0 only under a sliding window)
+  int n0, n1;  // KV tiles Q tile 0 / Q tile 1 visit, counted from `lo`
 };
+template <bool kWindow>
 __device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
   Item it;
   const int n_groups = p.batch * p.n_kv_head;
@@ -120,8 +124,12 @@ __device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
   it.row0 = it.mblk * 2 * kBM;
   const int nkv_total = (p.kv_seq + kBN - 1) / kBN;
   // KV tiles each Q tile visits.  Top-left causal: tile m needs keys <= its last row.
-  it.n0 = p.causal ? min(nkv_total, 2 * it.mblk + 1) : nkv_total;
-  it.n1 = p.causal ? min(nkv_total, 2 * it.mblk + 2) : nkv_total;
+  // Sliding window: the first row of the item sees no key before row0 - window + 1.  Both
+  // Q tiles start at that tile; a tile that lies wholly before a row's window is masked
+  // out for that row (the softmax copes with rows that have seen no key yet).
+  it.lo = kWindow ? max(0, it.row0 - p.window + 1) / kBN : 0;
+  it.n0 = (p.causal ? min(nkv_total, 2 * it.mblk + 1) : nkv_total) - it.lo;
+  it.n1 = (p.causal ? min(nkv_total, 2 * it.mblk + 2) : nkv_total) - it.lo;
   return it;
 }
 
@@ -193,7 +201,8 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
 // run on across items (every role counts its own uses), tensor memory and the
 // barriers are set up once, the next item's Q/K loads and first QK^T overlap the
 // previous item's epilogue.
-template <int D, int kPoly>
+// kWindow compiles the sliding-window mask in; the plain kernel carries none of its checks.
+template <int D, int kPoly, bool kWindow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -242,7 +251,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item(w, p);
+          const Item im = decode_item<kWindow>(w, p);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (it > 0) ok = ok && mbar_wait(bar(B::q_empty + t), (it - 1) & 1, abortp);
@@ -261,7 +270,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
             for (int kb = 0; kb < C::kBoxes; ++kb)
               tma_load_4d(sK + s * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(B::k_full + s), kb * 64,
-                          j * kBN, im.hkv, im.b);
+                          (im.lo + j) * kBN, im.hkv, im.b);
             ++kc;
           };
           auto load_v = [&](int j) {
@@ -272,7 +281,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
             for (int kb = 0; kb < C::kBoxes; ++kb)
               tma_load_4d(sV + s * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(B::v_full + s), kb * 64,
-                          j * kBN, im.hkv, im.b);
+                          (im.lo + j) * kBN, im.hkv, im.b);
             ++vc;
           };
           if (ok) load_k(0);
@@ -293,7 +302,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item(w, p);
+          const Item im = decode_item<kWindow>(w, p);
           const int n0 = im.n0, n1 = im.n1;
           ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
                mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
@@ -375,7 +384,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int it = 0; ok; ++it) {
       const int w = snake_item(it, total_items, p.snake);
       if (w < 0) break;
-      const Item im = decode_item(w, p);
+      const Item im = decode_item<kWindow>(w, p);
       const int row = im.row0 + t * kBM + r;  // query index
       const int n_t = t ? im.n1 : im.n0;
       float m_ref = -INFINITY, l = 0.f;
@@ -392,13 +401,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) tmem_ld_ready(sr[c]);
 
-        // keys this row may see in this tile: [0, limit)
-        int limit = p.kv_seq - j * kBN;
-        if (p.causal) limit = min(limit, row + 1 - j * kBN);
-        if (limit < kBN) {
+        // keys this row may see in this tile: [first, limit)
+        const int key0 = (im.lo + j) * kBN;
+        int limit = p.kv_seq - key0;
+        if (p.causal) limit = min(limit, row + 1 - key0);
+        const int first = kWindow ? row - p.window + 1 - key0 : 0;
+        if (limit < kBN || first > 0) {
 #pragma unroll
           for (int c = 0; c < kBN; ++c)
-            if (c >= limit) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+            if (c >= limit || c < first) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
         }
         float mxa[4];
 #pragma unroll
@@ -421,7 +432,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (__any_sync(0xffffffffu, grow)) {
             // PV_t(j-1) has completed (s_full covers it) and PV_t(j) is not issued
             // before this warp arrives on p_half, so O_t is ours to rescale.
-            const float alpha = ex2_approx((m_ref - m_new) * sl2);
+            // a row that has seen no key yet (m_new still -inf, sliding window only) keeps its zeros
+            const float alpha = (kWindow && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl2);
             l *= alpha;
             m_ref = m_new;
 #pragma unroll
@@ -436,7 +448,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
-        const float neg = -m_ref * sl2;
+        const float neg = (kWindow && m_ref == -INFINITY) ? 0.0f : -m_ref * sl2;  // all -inf scores give P = 0
         const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
         uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
@@ -568,7 +580,7 @@ int sm_count() {
   return n;
 }
 
-template <int D, int kPoly>
+template <int D, int kPoly, bool kWindow>
 int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv;
@@ -578,7 +590,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   if ((rc = make_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
   // per-device attribute: set on every launch so that any current device is covered
   cudaError_t attr_err = cudaFuncSetAttribute(
-      prefill_kernel<D, kPoly>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
+      prefill_kernel<D, kPoly, kWindow>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
   if (attr_err != cudaSuccess) return (int)attr_err;
   PrefillParams p;
   p.o = static_cast<__nv_bfloat16*>(a.o);
@@ -607,13 +619,14 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.q_seq = a.q_seq;
   p.kv_seq = a.kv_seq;
   p.group = a.n_head / a.n_kv_head;
-  p.causal = a.is_causal;
+  p.causal = (a.is_causal || a.window_size > 0) ? 1 : 0;
+  p.window = a.window_size > 0 ? a.window_size : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   const long long items = (long long)p.n_mblk * a.n_head * a.batch;
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   const int grid = (int)std::min<long long>(items, sm_count());
-  prefill_kernel<D, kPoly><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p);
+  prefill_kernel<D, kPoly, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -621,8 +634,9 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 }  // namespace
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
-  if (a.head_dim == 128) return launch<128, 0>(a, scale, status, st);
-  if (a.head_dim == 64) return launch<64, 0>(a, scale, status, st);
+  const bool win = a.window_size > 0;
+  if (a.head_dim == 128) return win ? launch<128, 0, true>(a, scale, status, st) : launch<128, 0, false>(a, scale, status, st);
+  if (a.head_dim == 64) return win ? launch<64, 0, true>(a, scale, status, st) : launch<64, 0, false>(a, scale, status, st);
   return -TYR_ATTN_ERR_HEAD_DIM;
 }
 

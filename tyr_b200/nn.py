@@ -38,7 +38,7 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise ValueError("tensor must have unit stride on the head dimension")
 
 
-def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode) -> PrefillArgs:
+def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode, window_size=0) -> PrefillArgs:
     B, Hq, Sq, D = q.shape
     Bk, Hkv, Skv, Dk = k.shape
     if v.shape != k.shape or Bk != B or Dk != D or o.shape != q.shape:
@@ -58,19 +58,22 @@ def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode) -> PrefillArgs:
     for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", o)):
         getattr(a, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
     a.dtype, a.is_causal, a.scale, a.check_mode = dtype, int(bool(is_causal)), float(scale or 0.0), int(bool(check_mode))
+    a.window_size = int(window_size)
     return a
 
 
 def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                  lse: Optional[torch.Tensor] = None, return_lse: bool = True,
-                 check_mode: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                 check_mode: bool = False, window_size: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """O = softmax(Q K^T * scale + causal) V and the per-row LSE.
 
     q [B,Hq,Sq,D]; k, v [B,Hkv,Skv,D] (Hq % Hkv == 0, query head h reads KV head
     h // (Hq/Hkv) as repeat_interleave does, cc/src/tyr.cpp:3931-3938).  Strided
     views are accepted (unit inner stride), e.g. the KV-cache slice of
     Tyr/Model/Qwen/Attention.lean:195-196.  `check_mode` runs the fp32-FMA kernel.
+    `window_size` > 0 adds the causal sliding window of lean_torch_sdpa_gqa_window
+    (cc/src/tyr.cpp:3986-3996): key j is visible to query i only if j <= i and i - j < window_size.
     Launcher convention of Examples/GPU/RunFlashAttn.lean:68-81: outputs may be
     pre-allocated by the caller and are written in place.
     """
@@ -84,7 +87,7 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous()
                             or tuple(lse.shape) != tuple(q.shape[:3])):
         raise ValueError("lse must be a contiguous float32 [batch, n_head, q_seq] tensor")
-    a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode)
+    a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode, window_size)
     with torch.cuda.device(q.device):
         check(_lib.load().tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
     return out, lse
@@ -117,6 +120,20 @@ def scaledDotProductAttentionGQAQKV(query, key, value, dropout_p: float = 0.0, i
                                     enable_gqa: bool = False):
     """Tyr/Torch.lean:1069-1082 -> lean_torch_sdpa_gqa_qkv (cc/src/tyr.cpp:4100-4133)."""
     return _sdpa(query, key, value, dropout_p, is_causal, enable_gqa)
+
+
+def scaledDotProductAttentionGQAWindow(query, key, value, dropout_p: float = 0.0, is_causal: bool = True,
+                                       enable_gqa: bool = False, window_size: int = 1):
+    """Tyr/Torch.lean:1084-1101 -> lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3953-4018).
+    As in the reference, the mask is always causal | window whatever `is_causal` says."""
+    if dropout_p != 0.0:
+        raise AttnError(-6)
+    if (not enable_gqa and query.shape[1] != key.shape[1]) or window_size <= 0:
+        raise AttnError(-2)
+    if query.shape[2] != key.shape[2]:
+        raise ValueError("scaledDotProductAttentionGQAWindow needs q_seq == kv_seq")
+    out, _ = attentionFwd(query, key, value, is_causal=True, return_lse=False, window_size=window_size)
+    return out
 
 
 def sdpa_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
