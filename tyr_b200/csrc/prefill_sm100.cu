@@ -50,7 +50,9 @@ struct PrefillParams {
   int64_t lse_stride_b, lse_stride_h;
   int q_seq, kv_seq, group, causal;
   int window;  // 0: none; > 0: key j visible to query i only while i - j < window (causal)
-  int n_head, batch, n_mblk;  // work items: n_mblk x n_head x batch
+  int n_head, batch, n_mblk;  // work items: n_mblk x heads_per_group_items x groups
+  int pair_heads;             // 1: an item is one 128-row block of TWO query heads of a KV head
+  int items_per_group;        // items per (batch, KV head): n_mblk * group (/ 2 when pairing heads)
   int n_kv_head, groups_per_chunk;  // (batch, KV head) groups whose K/V share L2 at one time
   int snake;  // 1: odd rounds of the static schedule are mirrored
   float scale_log2;           // scale * log2(e)
@@ -101,35 +103,53 @@ struct Bars {
 // balanced and the light items fill the tail), and the query heads that share a KV
 // head are neighbours, so CTAs running at the same time read the same K/V tiles.
 struct Item {
-  int mblk, hq, b, hkv, row0;
+  int mblk, b, hkv;
+  int hq[2];   // query head of Q tile 0 / 1
+  int row[2];  // first query row of Q tile 0 / 1
   int lo;      // first KV tile of the item (> 0 only under a sliding window)
   int n0, n1;  // KV tiles Q tile 0 / Q tile 1 visit, counted from `lo`
 };
+// Two ways to fill the two Q-tile slots of an item:
+//  rows  : 256 consecutive rows of one query head (tile 1 sits 128 rows below tile 0);
+//  heads : the same 128 rows of two query heads that share a KV head (GQA).  Both tiles
+//          then visit exactly the same K/V tiles, so under a causal mask neither waits
+//          for the other's extra diagonal tile, and a short query block wastes no slot.
 template <bool kWindow>
 __device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
   Item it;
   const int n_groups = p.batch * p.n_kv_head;
-  const int items_per_group = p.n_mblk * p.group;
+  const int items_per_group = p.items_per_group;
+  const int heads_per_level = p.pair_heads ? p.group / 2 : p.group;  // items per row block per group
   const int chunk = w / (p.groups_per_chunk * items_per_group);
   const int within = w - chunk * p.groups_per_chunk * items_per_group;
   const int g0 = chunk * p.groups_per_chunk;
   const int groups_here = min(p.groups_per_chunk, n_groups - g0);
-  const int per_level = groups_here * p.group;
+  const int per_level = groups_here * heads_per_level;
   it.mblk = p.n_mblk - 1 - within / per_level;
   const int idx = within % per_level;
-  const int gi = g0 + idx / p.group;
+  const int gi = g0 + idx / heads_per_level;
   it.b = gi / p.n_kv_head;
   it.hkv = gi % p.n_kv_head;
-  it.hq = it.hkv * p.group + idx % p.group;
-  it.row0 = it.mblk * 2 * kBM;
   const int nkv_total = (p.kv_seq + kBN - 1) / kBN;
-  // KV tiles each Q tile visits.  Top-left causal: tile m needs keys <= its last row.
-  // Sliding window: the first row of the item sees no key before row0 - window + 1.  Both
+  int last0, last1;  // last KV tile (exclusive) under a causal mask
+  if (p.pair_heads) {
+    it.hq[0] = it.hkv * p.group + 2 * (idx % heads_per_level);
+    it.hq[1] = it.hq[0] + 1;
+    it.row[0] = it.row[1] = it.mblk * kBM;
+    last0 = last1 = it.mblk + 1;
+  } else {
+    it.hq[0] = it.hq[1] = it.hkv * p.group + idx % heads_per_level;
+    it.row[0] = it.mblk * 2 * kBM;
+    it.row[1] = it.row[0] + kBM;
+    last0 = 2 * it.mblk + 1;  // top-left causal: a tile needs the keys up to its last row
+    last1 = 2 * it.mblk + 2;
+  }
+  // Sliding window: the first row of the item sees no key before row - window + 1.  Both
   // Q tiles start at that tile; a tile that lies wholly before a row's window is masked
   // out for that row (the softmax copes with rows that have seen no key yet).
-  it.lo = kWindow ? max(0, it.row0 - p.window + 1) / kBN : 0;
-  it.n0 = (p.causal ? min(nkv_total, 2 * it.mblk + 1) : nkv_total) - it.lo;
-  it.n1 = (p.causal ? min(nkv_total, 2 * it.mblk + 2) : nkv_total) - it.lo;
+  it.lo = kWindow ? max(0, it.row[0] - p.window + 1) / kBN : 0;
+  it.n0 = (p.causal ? min(nkv_total, last0) : nkv_total) - it.lo;
+  it.n1 = (p.causal ? min(nkv_total, last1) : nkv_total) - it.lo;
   return it;
 }
 
@@ -219,7 +239,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_items = p.n_mblk * p.n_head * p.batch;
+  const int total_items = p.items_per_group * p.n_kv_head * p.batch;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -260,7 +280,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
             for (int kb = 0; kb < C::kBoxes; ++kb)
               tma_load_4d(sQ + t * C::kTileBytes + kb * C::kBoxBytes, &tm_q, bar(B::q_full + t), kb * 64,
-                          im.row0 + t * kBM, im.hq, im.b);
+                          im.row[t], im.hq[t], im.b);
           }
           auto load_k = [&](int j) {
             const int s = kc % C::kKStages;
@@ -385,7 +405,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int w = snake_item(it, total_items, p.snake);
       if (w < 0) break;
       const Item im = decode_item<kWindow>(w, p);
-      const int row = im.row0 + t * kBM + r;  // query index
+      const int row = im.row[t] + r;  // query index
       const int n_t = t ? im.n1 : im.n0;
       float m_ref = -INFINITY, l = 0.f;
 
@@ -483,7 +503,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after();
       const float inv_l = 1.0f / l;
       const bool row_ok = row < p.q_seq;
-      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + im.hq * p.o_stride_h + (int64_t)row * p.o_stride_s;
+      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + im.hq[t] * p.o_stride_h + (int64_t)row * p.o_stride_s;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -501,7 +521,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       if (p.lse != nullptr && row_ok)
-        p.lse[im.b * p.lse_stride_b + im.hq * p.lse_stride_h + row] =
+        p.lse[im.b * p.lse_stride_b + im.hq[t] * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
       // O_t is read: order these loads before the next item's first PV_t, which this
       // warp gates through p_half
@@ -599,7 +619,13 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.o_stride_s = a.o_stride[2];
   p.n_head = a.n_head;
   p.batch = a.batch;
-  p.n_mblk = (a.q_seq + 2 * kBM - 1) / (2 * kBM);
+  {
+    const int group = a.n_head / a.n_kv_head;
+    // pair two heads of a KV head when that removes idle slots: causal masks, short query blocks
+    p.pair_heads = (group % 2 == 0 && (a.is_causal || a.window_size > 0 || a.q_seq <= kBM)) ? 1 : 0;
+    p.n_mblk = p.pair_heads ? (a.q_seq + kBM - 1) / kBM : (a.q_seq + 2 * kBM - 1) / (2 * kBM);
+    p.items_per_group = p.n_mblk * (p.pair_heads ? group / 2 : group);
+  }
   p.n_kv_head = a.n_kv_head;
   {
     // K and V of one (batch, KV head) group.  If all groups fit in L2 together (96 MB of
@@ -623,7 +649,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.window = a.window_size > 0 ? a.window_size : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  const long long items = (long long)p.n_mblk * a.n_head * a.batch;
+  const long long items = (long long)p.items_per_group * a.n_kv_head * a.batch;
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   const int grid = (int)std::min<long long>(items, sm_count());
   prefill_kernel<D, kPoly, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p);
