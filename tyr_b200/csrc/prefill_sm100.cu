@@ -165,31 +165,33 @@ __device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
   return w < total_items ? (int)w : -2;
 }
 
+// The issuing thread shares its SM sub-partition with two softmax warps, so every
+// instruction it spends per MMA delays the tensor pipe: descriptors are built once per
+// tile and stage, and each MMA only adds a compile-time constant to the address field.
 template <int D>
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem) {
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint64_t q_desc, uint64_t k_desc) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, false);
 #pragma unroll
   for (int kb = 0; kb < D / 64; ++kb) {
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      const uint32_t off = kb * Cfg<D>::kBoxBytes + ks * 32;
-      umma_ss(s_tmem, umma_smem_desc(q_smem + off, 16, 1024), umma_smem_desc(k_smem + off, 16, 1024),
-              idesc, (kb | ks) != 0);
+      const uint64_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
+      umma_ss(s_tmem, q_desc + off, k_desc + off, idesc, (kb | ks) != 0);
     }
   }
 }
 
 // `half` selects keys [64*half, 64*half + 64) of the tile.
 template <int D>
-__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem,
+__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc,
                                          bool accumulate, int half) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
 #pragma unroll
   for (int k4 = 0; k4 < kBN / 32; ++k4) {
     const int kk = half * (kBN / 32) + k4;
     // 16 keys = two 8-row groups of the V tile; 16 bf16 of P = 8 TMEM columns
-    umma_ts(o_tmem, p_tmem + kk * 8, umma_smem_desc(v_smem + kk * 2048, Cfg<D>::kBoxBytes, 1024),
-            idesc, (accumulate || kk != 0) ? 1u : 0u);
+    umma_ts(o_tmem, p_tmem + kk * 8, v_desc + ((kk * 2048) >> 4), idesc,
+            (accumulate || kk != 0) ? 1u : 0u);
   }
 }
 
@@ -316,6 +318,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (lane == 0) {
         const uint32_t tS0 = tmem + C::kTmemS, tS1 = tS0 + kBN;
         const uint32_t tO0 = tmem + C::kTmemO, tO1 = tO0 + D;
+        const uint64_t q_desc0 = umma_smem_desc(sQ, 16, 1024);
+        const uint64_t q_desc1 = umma_smem_desc(sQ + C::kTileBytes, 16, 1024);
         bool ok = true;
         int kc = 0, vc = 0;      // K / V tiles consumed so far
         int pc0 = 0, pc1 = 0;    // P tiles consumed so far, per Q tile
@@ -330,10 +334,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_after();
           {
             const int s = kc % C::kKStages;
-            issue_qk<D>(tS0, sQ, sK + s * C::kTileBytes);
+            const uint64_t k_desc = umma_smem_desc(sK + s * C::kTileBytes, 16, 1024);
+            issue_qk<D>(tS0, q_desc0, k_desc);
             umma_commit(bar(B::s_full + 0));
             if (n0 == 1) umma_commit(bar(B::q_empty + 0));
-            issue_qk<D>(tS1, sQ + C::kTileBytes, sK + s * C::kTileBytes);
+            issue_qk<D>(tS1, q_desc1, k_desc);
             umma_commit(bar(B::s_full + 1));
             if (n1 == 1) umma_commit(bar(B::q_empty + 1));
             umma_commit(bar(B::k_empty + s));
@@ -346,8 +351,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
             if (ok && next) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
             if (!ok) break;
-            const uint32_t v_smem = sV + vs * C::kTileBytes;
-            const uint32_t k_smem = sK + ks * C::kTileBytes;
+            const uint64_t v_smem = umma_smem_desc(sV + vs * C::kTileBytes, C::kBoxBytes, 1024);
+            const uint64_t k_smem = umma_smem_desc(sK + ks * C::kTileBytes, 16, 1024);
             if (j < n0) {
               ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
               if (!ok) break;
@@ -361,7 +366,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
             }
             if (j + 1 < n0) {
-              issue_qk<D>(tS0, sQ, k_smem);
+              issue_qk<D>(tS0, q_desc0, k_smem);
               umma_commit(bar(B::s_full + 0));
               if (j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
             }
@@ -378,7 +383,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ++vc;
             if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
             if (next) {
-              issue_qk<D>(tS1, sQ + C::kTileBytes, k_smem);
+              issue_qk<D>(tS1, q_desc1, k_smem);
               umma_commit(bar(B::s_full + 1));
               if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
               umma_commit(bar(B::k_empty + ks));
