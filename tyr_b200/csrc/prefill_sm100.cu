@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -576,8 +577,47 @@ EncodeTiledFn encode_fn() {
 }
 
 // [batch, heads, seq, D] bf16 with element strides {sb, sh, ss}; box = 64 x 128 rows, 128B swizzle.
+// Encoding a tensor map is pure host arithmetic on (pointer, sizes, strides); a model calls
+// the operator with the same few tensors over and over, so each thread keeps the last few.
+struct MapKey {
+  const void* ptr;
+  int batch, heads, seq, d;
+  int64_t stride[3];
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && batch == o.batch && heads == o.heads && seq == o.seq && d == o.d &&
+           stride[0] == o.stride[0] && stride[1] == o.stride[1] && stride[2] == o.stride[2];
+  }
+};
+constexpr int kMapCache = 16;
+struct MapCache {
+  MapKey key[kMapCache];
+  CUtensorMap map[kMapCache];
+  int used = 0, next = 0;
+};
+
+int encode_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d,
+               const int64_t* stride);
+
 int make_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d,
              const int64_t* stride) {
+  static thread_local MapCache cache;
+  const MapKey k{ptr, batch, heads, seq, d, {stride[0], stride[1], stride[2]}};
+  for (int i = 0; i < cache.used; ++i)
+    if (cache.key[i] == k) {
+      *m = cache.map[i];
+      return 0;
+    }
+  const int rc = encode_map(m, ptr, batch, heads, seq, d, stride);
+  if (rc) return rc;
+  cache.key[cache.next] = k;
+  cache.map[cache.next] = *m;
+  cache.next = (cache.next + 1) % kMapCache;
+  if (cache.used < kMapCache) ++cache.used;
+  return 0;
+}
+
+int encode_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d,
+               const int64_t* stride) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -TYR_ATTN_ERR_NO_DEVICE;
   cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
@@ -613,10 +653,19 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   if ((rc = make_map(&tq, a.q, a.batch, a.n_head, a.q_seq, D, a.q_stride))) return rc;
   if ((rc = make_map(&tk, a.k, a.batch, a.n_kv_head, a.kv_seq, D, a.k_stride))) return rc;
   if ((rc = make_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
-  // per-device attribute: set on every launch so that any current device is covered
-  cudaError_t attr_err = cudaFuncSetAttribute(
-      prefill_kernel<D, kPoly, kWindow>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes);
-  if (attr_err != cudaSuccess) return (int)attr_err;
+  {
+    // per-device attribute, set once per device and kernel instantiation
+    static std::atomic<bool> attr_set[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
+      cudaError_t attr_err = cudaFuncSetAttribute(prefill_kernel<D, kPoly, kWindow>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)C::kSmemBytes);
+      if (attr_err != cudaSuccess) return (int)attr_err;
+      attr_set[dev].store(true, std::memory_order_release);
+    }
+  }
   PrefillParams p;
   p.o = static_cast<__nv_bfloat16*>(a.o);
   p.o_stride_b = a.o_stride[0];
