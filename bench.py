@@ -232,6 +232,43 @@ def other_workloads(tnn, dev, peaks, steps=10, warmup=3):
     return out
 
 
+def sharded_workloads(tnn, dev, rank, world, barrier, all_max, steps=10, warmup=3):
+    """Strong scaling at N > 1: ONE fixed workload cut across the ranks by the shard rules of
+    tyr_b200/partition.py (KV-head groups, else batch; LPT split for decode), no collective on
+    the data path.  Time = max over ranks of the device time; value = whole-job work / time."""
+    from tyr_b200 import partition as P
+    out = {}
+    for name in ("qwen3_8b_prefill", "flux_mmdit"):
+        w = W.WORKLOADS[name]
+        sh = P.prefill_shard(w.batch, w.n_kv_head, world, rank)
+        g_ = w.n_head // w.n_kv_head
+        nb, nh = sh.batch[1] - sh.batch[0], sh.kv_heads[1] - sh.kv_heads[0]
+        gen = torch.Generator(device=dev).manual_seed(w.seed + rank)
+        q = torch.randn(nb, nh * g_, w.seq, w.head_dim, device=dev, generator=gen).bfloat16()
+        k = torch.randn(nb, nh, w.seq, w.head_dim, device=dev, generator=gen).bfloat16()
+        v = torch.randn(nb, nh, w.seq, w.head_dim, device=dev, generator=gen).bfloat16()
+        o, lse = torch.empty_like(q), torch.empty(q.shape[:3], device=dev)
+        sec = all_max(time_events(lambda: tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse),
+                                  steps, warmup, barrier) / steps)
+        out[name] = {"ms": sec * 1e3, "tflops": w.flops / sec / 1e12, "shard_axis": sh.axis,
+                     "shard": f"batch {nb} x kv_heads {nh} per GPU"}
+        del q, k, v, o, lse
+    w = W.WORKLOADS["qwen3_8b_decode"]
+    lens = W.decode_lengths(w)
+    mine = P.lpt_partition(lens, world)[rank]
+    gen = torch.Generator(device=dev).manual_seed(w.seed + rank)
+    ks = [torch.randn(w.n_kv_head, lens[i], w.head_dim, device=dev, generator=gen).bfloat16() for i in mine]
+    vs = [torch.randn(w.n_kv_head, lens[i], w.head_dim, device=dev, generator=gen).bfloat16() for i in mine]
+    q = torch.randn(len(mine), w.n_head, w.head_dim, device=dev, generator=gen).bfloat16()
+    plan = tnn.DecodePlan(ks, vs, w.n_head)
+    o, lse = torch.empty_like(q), torch.empty(q.shape[:2], device=dev)
+    sec = all_max(time_events(lambda: tnn.flashDecode(q, plan, out=o, lse=lse), steps, warmup, barrier) / steps)
+    byts = W.decode_kv_bytes(lens, w.n_kv_head, w.head_dim)
+    out[w.name] = {"ms": sec * 1e3, "kv_gbs": byts / sec / 1e9, "shard": "sequences by greedy length-balanced split",
+                   "sequences_on_rank0": len(mine)}
+    return out
+
+
 def run_profile(args):
     """warm-up + steps launches of one kernel and nothing else (for ncu captures)."""
     from tyr_b200 import nn as tnn
@@ -330,6 +367,16 @@ def run_ours(args):
     h2d = (qh.numel() + kh.numel() + vh.numel()) * 2
     d2h = oh.numel() * 2 + lseh.numel() * 4
 
+    def all_max(x):
+        tt = torch.tensor([x], dtype=torch.float64, device=dev)
+        if use_dist:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    sharded = None
+    if use_dist and not args.no_others:
+        sharded = sharded_workloads(tnn, dev, rank, world, barrier, all_max)
+
     line = None
     if rank == 0:
         cpu = None
@@ -366,6 +413,8 @@ def run_ours(args):
         }
         if others is not None:
             line["other_workloads"] = others
+        if sharded is not None:
+            line["strong_scaling_sharded"] = sharded
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()
