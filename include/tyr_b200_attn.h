@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 2
+#define TYR_ATTN_ABI_VERSION 3
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -74,6 +74,12 @@ typedef struct TyrAttnPrefillArgs {
   int32_t window_size; /* 0 => none; w > 0 => key j is visible to query i only if j <= i and
                           i - j < w (implies is_causal), the mask lean_torch_sdpa_gqa_window
                           builds at cc/src/tyr.cpp:3986-3996 */
+  const uint8_t* key_mask; /* NULL, or DEVICE bytes [batch, kv_seq]: 0 marks a padding key that
+                              no query sees, any other value a valid key — the key/value part
+                              of the padding mask of lean_torch_sdpa_gqa_mask
+                              (cc/src/tyr.cpp:4063-4086).  A query that sees no key at all
+                              gets NaN output, as it does from ATen. */
+  int64_t key_mask_stride; /* bytes between the mask rows of two batch elements */
 } TyrAttnPrefillArgs;
 
 int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* args, void* stream);
@@ -104,6 +110,13 @@ int tyr_b200_sdpa_gqa_window(uint64_t batch, uint64_t n_head, uint64_t n_kv_head
                              uint64_t head_dim, const void* q, const void* k, const void* v,
                              void* out, double dropout_p, uint8_t is_causal, uint8_t enable_gqa,
                              uint64_t window_size, void* stream);
+/* tyr_b200_sdpa_gqa_mask <- lean_torch_sdpa_gqa_mask cc/src/tyr.cpp:4024-4095: padding mask
+ * [batch, seq] over the keys (here as one byte per key, non-zero = valid), optionally combined
+ * with the causal mask.  No [batch, 1, seq, seq] mask tensor is built. */
+int tyr_b200_sdpa_gqa_mask(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                           uint64_t head_dim, const void* q, const void* k, const void* v,
+                           const uint8_t* key_mask, void* out, double dropout_p, uint8_t is_causal,
+                           uint8_t enable_gqa, void* stream);
 
 /* ------------------------------------------------------------------------
  * Decode: one query token per sequence over a (possibly ragged) KV cache,

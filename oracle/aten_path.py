@@ -47,6 +47,30 @@ def sdpa_gqa_window(q, k, v, dropout_p: float = 0.0, is_causal: bool = True, ena
     return F.scaled_dot_product_attention(q, k, v, mask, dropout_p, False)
 
 
+def sdpa_gqa_mask(q, k, v, padding_mask, dropout_p: float = 0.0, is_causal: bool = True,
+                  enable_gqa: bool = True):
+    """cc/src/tyr.cpp:4024-4095 (lean_torch_sdpa_gqa_mask): padding_mask [batch, seq], 1 = valid
+    key, 0 = padding; turned into a -inf/0 mask (with the causal mask when asked) for SDPA."""
+    n_head, n_kv_head = q.shape[1], k.shape[1]
+    if enable_gqa and n_head != n_kv_head and n_kv_head > 0:
+        rep = n_head // n_kv_head
+        k = k.repeat_interleave(rep, 1)
+        v = v.repeat_interleave(rep, 1)
+    seq = q.shape[2]
+    key_mask = padding_mask.unsqueeze(1).unsqueeze(2)
+    ninf = float("-inf")
+    if is_causal:
+        row = torch.arange(seq).unsqueeze(1)
+        col = torch.arange(seq).unsqueeze(0)
+        combined = (col > row).unsqueeze(0).unsqueeze(0) | (key_mask == 0)
+        mask = torch.where(combined, torch.full((1, 1, seq, seq), ninf, dtype=q.dtype),
+                           torch.zeros((1, 1, seq, seq), dtype=q.dtype))
+    else:
+        mask = torch.where(key_mask == 0, torch.full((1, 1, 1, seq), ninf, dtype=q.dtype),
+                           torch.zeros((1, 1, 1, seq), dtype=q.dtype))
+    return F.scaled_dot_product_attention(q, k, v, mask, dropout_p, False)
+
+
 def lse(q, k, v, is_causal: bool):
     """Natural-log LSE of the scaled scores, [B,Hq,Sq] fp32, from ATen's CPU flash kernel."""
     n_head, n_kv_head = q.shape[1], k.shape[1]

@@ -20,6 +20,8 @@
  *                          LSE = log(sum(exp(scaled scores))) (RunFlashAttn.lean:45-48).
  *   tyr_oracle_sdpa_window the same with the causal sliding-window mask of
  *                          lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3953-4018).
+ *   tyr_oracle_sdpa_keymask the same with the key padding mask of lean_torch_sdpa_gqa_mask
+ *                          (cc/src/tyr.cpp:4024-4095).
  *   tyr_oracle_sdpa_online the running max / running sum form of
  *                          Tyr/GPU/Codegen/Macros.lean:121-163 with fp32 state.
  *   tyr_oracle_merge2      LSE merge of two partial results,
@@ -74,7 +76,7 @@ void tyr_oracle_bf16_round(const float* in, float* out, int64_t n) {
  * when i - j >= window; that entry point always combines it with the causal mask. */
 static int sdpa_direct(const float* q, const float* k, const float* v, float* o, float* lse, int B,
                        int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale,
-                       int window) {
+                       int window, const uint8_t* key_mask) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0) return -1;
   const int g = Hq / Hkv; /* query head h reads KV head h / g */
   const int64_t rows = (int64_t)B * Hq * Sq;
@@ -103,12 +105,13 @@ static int sdpa_direct(const float* q, const float* k, const float* v, float* o,
           double dot = 0.0;
           for (int d = 0; d < D; ++d) dot += (double)qr[d] * (double)kr[d];
           s[j] = dot * (double)scale;
+          if (key_mask && key_mask[(int64_t)b * Skv + j] == 0) s[j] = -INFINITY; /* padding key */
           if (s[j] > mx) mx = s[j];
         }
         double sum = 0.0;
         for (int d = 0; d < D; ++d) acc[d] = 0.0;
         for (int j = j0; j < n; ++j) {
-          const double p = exp(s[j] - mx);
+          const double p = (s[j] == -INFINITY) ? 0.0 : exp(s[j] - mx);
           sum += p;
           const float* vr = vb + (int64_t)j * D;
           for (int d = 0; d < D; ++d) acc[d] += p * (double)vr[d];
@@ -125,13 +128,23 @@ static int sdpa_direct(const float* q, const float* k, const float* v, float* o,
 
 int tyr_oracle_sdpa(const float* q, const float* k, const float* v, float* o, float* lse, int B,
                     int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float scale) {
-  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, Sq, Skv, D, is_causal, scale, 0);
+  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, Sq, Skv, D, is_causal, scale, 0, NULL);
 }
 
 int tyr_oracle_sdpa_window(const float* q, const float* k, const float* v, float* o, float* lse,
                            int B, int Hq, int Hkv, int S, int D, float scale, int window) {
   if (window <= 0) return -1;
-  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, S, S, D, 1, scale, window);
+  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, S, S, D, 1, scale, window, NULL);
+}
+
+/* Padding mask of lean_torch_sdpa_gqa_mask (cc/src/tyr.cpp:4024-4095): key_mask [B, S] bytes,
+ * 0 = padding key hidden from every query, combined with the causal mask when is_causal.
+ * A query that sees no key gets 0/0 = NaN, as ATen's softmax over all -inf does. */
+int tyr_oracle_sdpa_keymask(const float* q, const float* k, const float* v, float* o, float* lse,
+                            int B, int Hq, int Hkv, int S, int D, int is_causal, float scale,
+                            const uint8_t* key_mask) {
+  if (!key_mask) return -1;
+  return sdpa_direct(q, k, v, o, lse, B, Hq, Hkv, S, S, D, is_causal, scale, 0, key_mask);
 }
 
 /* Online form with fp32 state, keys visited in blocks of `block` (Macros.lean:121-163):

@@ -29,6 +29,8 @@ def lib() -> ctypes.CDLL:
         L.tyr_oracle_sdpa.restype = ctypes.c_int
         L.tyr_oracle_sdpa_window.argtypes = [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int]
         L.tyr_oracle_sdpa_window.restype = ctypes.c_int
+        L.tyr_oracle_sdpa_keymask.argtypes = [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.POINTER(ctypes.c_uint8)]
+        L.tyr_oracle_sdpa_keymask.restype = ctypes.c_int
         L.tyr_oracle_sdpa_online.argtypes = (
             [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 7 + [ctypes.c_float, ctypes.c_int]
         )
@@ -58,7 +60,8 @@ def threads() -> int:
     return int(lib().tyr_oracle_threads())
 
 
-def sdpa(q, k, v, is_causal: bool, scale: float | None = None, online_block: int = 0, window: int = 0):
+def sdpa(q, k, v, is_causal: bool, scale: float | None = None, online_block: int = 0, window: int = 0,
+         key_mask=None):
     """q [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] fp32 -> (o [B,Hq,Sq,D], lse [B,Hq,Sq])."""
     q, k, v = _c(q), _c(k), _c(v)
     B, Hq, Sq, D = q.shape
@@ -68,7 +71,14 @@ def sdpa(q, k, v, is_causal: bool, scale: float | None = None, online_block: int
         scale = 1.0 / float(np.sqrt(D))
     o = np.empty_like(q)
     lse = np.empty((B, Hq, Sq), dtype=np.float32)
-    if window:
+    if key_mask is not None:
+        assert Sq == Skv and not window
+        km = np.ascontiguousarray(np.asarray(key_mask) != 0, dtype=np.uint8)
+        assert km.shape == (B, Skv)
+        rc = lib().tyr_oracle_sdpa_keymask(_p(q), _p(k), _p(v), _p(o), _p(lse), B, Hq, Hkv, Sq, D,
+                                           int(bool(is_causal)), scale,
+                                           km.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)))
+    elif window:
         assert Sq == Skv
         rc = lib().tyr_oracle_sdpa_window(_p(q), _p(k), _p(v), _p(o), _p(lse), B, Hq, Hkv, Sq, D, scale, int(window))
     elif online_block:

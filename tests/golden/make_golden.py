@@ -64,6 +64,24 @@ def main():
     print(path, os.path.getsize(path), "bytes")
 
 
+def main_keymask():
+    """tests/golden/aten_keymask.npz: lean_torch_sdpa_gqa_mask restated with torch (padding mask)."""
+    g = torch.Generator(device="cpu").manual_seed(3000)
+    B, Hq, Hkv, S, D = 2, 1, 1, 130, 64
+    q, k, v = (torch.randn(B, h, S, D, generator=g).bfloat16().float() for h in (Hq, Hkv, Hkv))
+    m = torch.ones(B, S)
+    m[0, 90:] = 0           # right padding
+    m[1, 20:45] = 0         # a hole
+    out = {"mask": m.numpy().astype(np.uint8), "torch_version": np.array(torch.__version__)}
+    for key, t in (("q", q), ("k", k), ("v", v)):
+        out[key] = (t.numpy().view(np.uint32) >> 16).astype(np.uint16)
+    out["o_causal"] = aten_path.sdpa_gqa_mask(q, k, v, m, 0.0, True, True).numpy()
+    out["o_full"] = aten_path.sdpa_gqa_mask(q, k, v, m, 0.0, False, True).numpy()
+    path = os.path.join(os.path.dirname(__file__), "aten_keymask.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes")
+
+
 def main_prologue():
     """tests/golden/aten_prologue.npz: the reference's op chain before attention (per-head
     RMSNorm, rotary embedding, transpose, cache slice_scatter) run with torch on fp32."""
@@ -88,3 +106,4 @@ def main_prologue():
 if __name__ == "__main__":
     main()
     main_prologue()
+    main_keymask()

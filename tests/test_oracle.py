@@ -166,3 +166,33 @@ def test_window_closed_forms():
     i = 20
     oi, _ = c_oracle.sdpa(q[:, :, i:i + 1], k[:, :, i - 4:i + 1], v[:, :, i - 4:i + 1], False)
     np.testing.assert_allclose(o5[:, :, i:i + 1], oi, rtol=1e-5, atol=1e-6)
+
+
+def _load_keymask_golden():
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_keymask.npz"))
+    f = lambda a: (a.astype(np.uint32) << 16).view(np.float32)
+    return f(g["q"]), f(g["k"]), f(g["v"]), g["mask"], g["o_causal"], g["o_full"]
+
+
+def test_keymask_oracle_matches_golden_reference_mask():
+    q, k, v, m, o_causal, o_full = _load_keymask_golden()
+    o, _ = c_oracle.sdpa(q, k, v, True, key_mask=m)
+    assert rel(o, o_causal) < 1e-5
+    o, _ = c_oracle.sdpa(q, k, v, False, key_mask=m)
+    assert rel(o, o_full) < 1e-5
+
+
+def test_keymask_closed_forms():
+    rng = np.random.default_rng(13)
+    q = rng.standard_normal((1, 1, 6, 16), dtype=np.float32)
+    k = rng.standard_normal((1, 1, 6, 16), dtype=np.float32)
+    v = rng.standard_normal((1, 1, 6, 16), dtype=np.float32)
+    m = np.array([[1, 1, 1, 0, 0, 0]], np.uint8)
+    o, lse = c_oracle.sdpa(q, k, v, False, key_mask=m)           # == attention over the 3 valid keys
+    o3, lse3 = c_oracle.sdpa(q, k[:, :, :3], v[:, :, :3], False)
+    np.testing.assert_allclose(o, o3, rtol=1e-6)
+    np.testing.assert_allclose(lse, lse3, rtol=1e-6)
+    m0 = np.array([[0, 1, 1, 1, 1, 1]], np.uint8)                # causal row 0 sees only a padding key
+    o, _ = c_oracle.sdpa(q, k, v, True, key_mask=m0)
+    assert np.isnan(o[0, 0, 0]).all() and not np.isnan(o[0, 0, 1:]).any()

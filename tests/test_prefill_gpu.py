@@ -78,6 +78,41 @@ def test_ragged_sequence_lengths(S, D, causal):
     assert_parity(o, lse, ro, rlse, (S, D, causal))
 
 
+@pytest.mark.parametrize("S", [150, 400, 1000])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_padding_key_mask(S, D, causal):
+    # lean_torch_sdpa_gqa_mask (cc/src/tyr.cpp:4024-4095): 0 in the [batch, seq] mask hides that key
+    B = 3
+    q, k, v = randn(B, 4, S, D, seed=S), randn(B, 2, S, D, seed=S + 1), randn(B, 2, S, D, seed=S + 2)
+    m = torch.ones(B, S, dtype=torch.uint8)
+    m[0, S // 2:] = 0                 # right padding, whole KV tiles masked out for long S
+    m[1, 5:S // 3] = 0                # a hole
+    m[2, 1::2] = 0                    # every other key
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=causal, key_mask=m.to(DEV))
+    ro, rlse = c_oracle.sdpa(q.float().numpy(), k.float().numpy(), v.float().numpy(), causal, key_mask=m.numpy())
+    assert_parity(o, lse, ro, rlse, (S, D, causal))
+    oc, lc = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=causal, key_mask=m.to(DEV), check_mode=True)
+    assert_parity(oc, lc, ro, rlse, ("check", S, D, causal))
+    o2 = tnn.scaledDotProductAttentionGQAMask(q.to(DEV), k.to(DEV), v.to(DEV), m.float().to(DEV), 0.0, causal, True)
+    assert torch.equal(o2, o)
+
+
+def test_padding_key_mask_golden_and_unseen_rows():
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_keymask.npz"))
+    f = lambda a: torch.tensor((a.astype(np.uint32) << 16).view(np.float32)).bfloat16().to(DEV)
+    q, k, v, m = f(g["q"]), f(g["k"]), f(g["v"]), torch.tensor(g["mask"]).to(DEV)
+    for causal, key in ((True, "o_causal"), (False, "o_full")):
+        o, _ = tnn.attentionFwd(q, k, v, is_causal=causal, key_mask=m)
+        assert_parity(o, None, g[key], None, key)
+    # a query that sees no key at all gets NaN, like ATen's softmax over all -inf
+    m0 = torch.ones(2, q.shape[2], dtype=torch.uint8)
+    m0[:, 0] = 0
+    o, _ = tnn.attentionFwd(q, k, v, is_causal=True, key_mask=m0.to(DEV))
+    assert torch.isnan(o[:, :, 0].float()).all() and not torch.isnan(o[:, :, 1:].float()).any()
+
+
 @pytest.mark.parametrize("Sq,Skv", [(1, 300), (5, 9), (100, 700), (300, 40), (129, 128)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_query_and_key_lengths_differ(Sq, Skv, causal):

@@ -7,8 +7,8 @@ include/tyr_b200_attn.h.  PyTorch is used for device memory and streams only.
 from . import nn  # noqa: F401
 from .nn import (attentionFwd, flashDecode, scaled_dot_product_attention,  # noqa: F401
                  scaledDotProductAttentionGQA, scaledDotProductAttentionGQAQKV,
-                 scaledDotProductAttentionGQAWindow)
+                 scaledDotProductAttentionGQAMask, scaledDotProductAttentionGQAWindow)
 
 __all__ = ["nn", "attentionFwd", "flashDecode", "scaled_dot_product_attention",
            "scaledDotProductAttentionGQA", "scaledDotProductAttentionGQAQKV",
-           "scaledDotProductAttentionGQAWindow"]
+           "scaledDotProductAttentionGQAWindow", "scaledDotProductAttentionGQAMask"]

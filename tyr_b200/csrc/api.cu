@@ -53,6 +53,7 @@ int check_prefill(const TyrAttnPrefillArgs* a) {
   if (a->dtype == TYR_ATTN_F32 && !a->check_mode) return -TYR_ATTN_ERR_DTYPE;
   if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
   if (a->window_size < 0) return -TYR_ATTN_ERR_SHAPE;
+  if (a->key_mask && a->batch > 1 && a->key_mask_stride < a->kv_seq) return -TYR_ATTN_ERR_SHAPE;
   if (!a->check_mode) {
     if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
     if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o))
@@ -80,7 +81,7 @@ void contiguous_strides(int64_t* s, int64_t heads, int64_t seq, int64_t d) {
 int sdpa_contiguous(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t q_seq,
                     uint64_t kv_seq, uint64_t head_dim, const void* q, const void* k, const void* v,
                     void* out, double dropout_p, uint8_t is_causal, void* stream,
-                    uint64_t window_size = 0) {
+                    uint64_t window_size = 0, const uint8_t* key_mask = nullptr) {
   if (dropout_p != 0.0) return -TYR_ATTN_ERR_DROPOUT;
   if (batch > 0x7fffffffu || n_head > 0x7fffffffu || n_kv_head > 0x7fffffffu ||
       q_seq > 0x7fffffffu || kv_seq > 0x7fffffffu || head_dim > 0x7fffffffu)
@@ -97,6 +98,8 @@ int sdpa_contiguous(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_
   a.dtype = TYR_ATTN_BF16;
   a.is_causal = is_causal ? 1 : 0;
   a.window_size = (int32_t)std::min<uint64_t>(window_size, 0x7fffffffu);
+  a.key_mask = key_mask;
+  a.key_mask_stride = (int64_t)kv_seq;
   return tyr_b200_attn_prefill(&a, stream);
 }
 
@@ -174,6 +177,16 @@ int tyr_b200_sdpa_gqa_window(uint64_t batch, uint64_t n_head, uint64_t n_kv_head
                          stream, window_size);
 }
 
+int tyr_b200_sdpa_gqa_mask(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, uint64_t seq,
+                           uint64_t head_dim, const void* q, const void* k, const void* v,
+                           const uint8_t* key_mask, void* out, double dropout_p, uint8_t is_causal,
+                           uint8_t enable_gqa, void* stream) {
+  if (!enable_gqa && n_head != n_kv_head) return -TYR_ATTN_ERR_SHAPE;
+  if (!key_mask) return -TYR_ATTN_ERR_NULL;
+  return sdpa_contiguous(batch, n_head, n_kv_head, seq, seq, head_dim, q, k, v, out, dropout_p,
+                         is_causal, stream, 0, key_mask);
+}
+
 size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim,
                                             int32_t max_kv_seq, int32_t max_splits) {
   if (batch <= 0 || n_head <= 0 || head_dim <= 0 || max_kv_seq <= 0) return 0;
@@ -227,6 +240,7 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   int rc = check_prefill(a);
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment
   if (device < 0 || device >= kMaxDevices) return -TYR_ATTN_ERR_NO_DEVICE;
+  if (a->key_mask) return -TYR_ATTN_ERR_DTYPE;  // the host-buffer call takes no padding mask
   const size_t es = a->dtype == TYR_ATTN_F32 ? 4 : 2;
   const size_t nq = (size_t)a->batch * a->n_head * a->q_seq * a->head_dim;
   const size_t nk = (size_t)a->batch * a->n_kv_head * a->kv_seq * a->head_dim;

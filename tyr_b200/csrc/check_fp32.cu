@@ -26,6 +26,8 @@ struct CheckParams {
   float* lse;
   int batch, n_head, n_kv_head, q_seq, kv_seq, d, causal, window;
   int64_t qs[3], ks[3], vs[3], os[3];
+  const uint8_t* key_mask;  // [batch, kv_seq], 0 = padding key; or null
+  int64_t key_mask_stride;
   float scale;
 };
 
@@ -59,7 +61,8 @@ check_kernel(const CheckParams p) {
   for (int k0 = key_lo; k0 < n_keys; k0 += 32) {
     const int key = k0 + lane;
     float s = -INFINITY;
-    if (key < n_keys) {
+    const bool seen = key < n_keys && (p.key_mask == nullptr || p.key_mask[b * p.key_mask_stride + key] != 0);
+    if (seen) {
       const T* kr = kbase + (int64_t)key * p.ks[2];
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(q_sh[warp][d], to_f32(kr[d]), dot);
@@ -70,7 +73,7 @@ check_kernel(const CheckParams p) {
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     const float m_new = fmaxf(m, mx);
     const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
-    const float pr = (key < n_keys) ? expf(s - m_new) : 0.f;
+    const float pr = (seen && m_new != -INFINITY) ? expf(s - m_new) : 0.f;
     float ps = pr;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
@@ -115,6 +118,8 @@ int launch_prefill_check(const TyrAttnPrefillArgs& a, float scale, cudaStream_t 
   p.q_seq = a.q_seq; p.kv_seq = a.kv_seq; p.d = a.head_dim;
   p.causal = (a.is_causal || a.window_size > 0) ? 1 : 0;
   p.window = a.window_size > 0 ? a.window_size : 0;
+  p.key_mask = a.key_mask;
+  p.key_mask_stride = a.key_mask_stride;
   for (int i = 0; i < 3; ++i) {
     p.qs[i] = a.q_stride[i]; p.ks[i] = a.k_stride[i]; p.vs[i] = a.v_stride[i]; p.os[i] = a.o_stride[i];
   }

@@ -51,6 +51,8 @@ struct PrefillParams {
   int64_t lse_stride_b, lse_stride_h;
   int q_seq, kv_seq, group, causal;
   int window;  // 0: none; > 0: key j visible to query i only while i - j < window (causal)
+  const uint8_t* key_mask;   // [batch, kv_seq] bytes, 0 = padding key hidden from every query; or null
+  int64_t key_mask_stride;
   int n_head, batch, n_mblk;  // work items: n_mblk x heads_per_group_items x groups
   int pair_heads;             // 1: an item is one 128-row block of TWO query heads of a KV head
   int items_per_group;        // items per (batch, KV head): n_mblk * group (/ 2 when pairing heads)
@@ -148,7 +150,7 @@ __device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
   // Sliding window: the first row of the item sees no key before row - window + 1.  Both
   // Q tiles start at that tile; a tile that lies wholly before a row's window is masked
   // out for that row (the softmax copes with rows that have seen no key yet).
-  it.lo = kWindow ? max(0, it.row[0] - p.window + 1) / kBN : 0;
+  it.lo = (kWindow && p.window > 0) ? max(0, it.row[0] - p.window + 1) / kBN : 0;
   it.n0 = (p.causal ? min(nkv_total, last0) : nkv_total) - it.lo;
   it.n1 = (p.causal ? min(nkv_total, last1) : nkv_total) - it.lo;
   return it;
@@ -224,7 +226,8 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
 // run on across items (every role counts its own uses), tensor memory and the
 // barriers are set up once, the next item's Q/K loads and first QK^T overlap the
 // previous item's epilogue.
-// kWindow compiles the sliding-window mask in; the plain kernel carries none of its checks.
+// kWindow compiles the sliding-window and padding-key masks in (rows may then meet tiles in
+// which they see no key); the plain kernel carries none of those checks.
 template <int D, int kPoly, bool kWindow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -431,11 +434,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int key0 = (im.lo + j) * kBN;
         int limit = p.kv_seq - key0;
         if (p.causal) limit = min(limit, row + 1 - key0);
-        const int first = kWindow ? row - p.window + 1 - key0 : 0;
+        const int first = (kWindow && p.window > 0) ? row - p.window + 1 - key0 : 0;
         if (limit < kBN || first > 0) {
 #pragma unroll
           for (int c = 0; c < kBN; ++c)
             if (c >= limit || c < first) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+        }
+        if (kWindow && p.key_mask != nullptr) {
+          // padding keys: lane i fetches the mask bytes of keys 4i..4i+3 of the tile, four
+          // ballots spread them to every row; key c is bit (c >> 2) of ballot (c & 3)
+          const uint8_t* mrow = p.key_mask + im.b * p.key_mask_stride + key0;
+          uint32_t vb[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int kk = 4 * lane + e;
+            const bool valid = (key0 + kk < p.kv_seq) && mrow[kk] != 0;
+            vb[e] = __ballot_sync(0xffffffffu, valid);
+          }
+#pragma unroll
+          for (int c = 0; c < kBN; ++c)
+            if (!((vb[c & 3] >> (c >> 2)) & 1u)) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
         }
         float mxa[4];
 #pragma unroll
@@ -701,6 +719,8 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.group = a.n_head / a.n_kv_head;
   p.causal = (a.is_causal || a.window_size > 0) ? 1 : 0;
   p.window = a.window_size > 0 ? a.window_size : 0;
+  p.key_mask = a.key_mask;
+  p.key_mask_stride = a.key_mask_stride;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   const long long items = (long long)p.items_per_group * a.n_kv_head * a.batch;
@@ -714,7 +734,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 }  // namespace
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
-  const bool win = a.window_size > 0;
+  const bool win = a.window_size > 0 || a.key_mask != nullptr;
   if (a.head_dim == 128) return win ? launch<128, 0, true>(a, scale, status, st) : launch<128, 0, false>(a, scale, status, st);
   if (a.head_dim == 64) return win ? launch<64, 0, true>(a, scale, status, st) : launch<64, 0, false>(a, scale, status, st);
   return -TYR_ATTN_ERR_HEAD_DIM;

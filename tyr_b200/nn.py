@@ -38,7 +38,7 @@ def _require_cuda(*ts: torch.Tensor) -> None:
             raise ValueError("tensor must have unit stride on the head dimension")
 
 
-def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode, window_size=0) -> PrefillArgs:
+def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode, window_size=0, key_mask=None) -> PrefillArgs:
     B, Hq, Sq, D = q.shape
     Bk, Hkv, Skv, Dk = k.shape
     if v.shape != k.shape or Bk != B or Dk != D or o.shape != q.shape:
@@ -59,13 +59,18 @@ def _fill_prefill(q, k, v, o, lse, is_causal, scale, check_mode, window_size=0) 
         getattr(a, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
     a.dtype, a.is_causal, a.scale, a.check_mode = dtype, int(bool(is_causal)), float(scale or 0.0), int(bool(check_mode))
     a.window_size = int(window_size)
+    if key_mask is not None:
+        a.key_mask, a.key_mask_stride = key_mask.data_ptr(), key_mask.stride(0)
+    else:
+        a.key_mask, a.key_mask_stride = None, 0
     return a
 
 
 def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True,
                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                  lse: Optional[torch.Tensor] = None, return_lse: bool = True,
-                 check_mode: bool = False, window_size: int = 0) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                 check_mode: bool = False, window_size: int = 0,
+                 key_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """O = softmax(Q K^T * scale + causal) V and the per-row LSE.
 
     q [B,Hq,Sq,D]; k, v [B,Hkv,Skv,D] (Hq % Hkv == 0, query head h reads KV head
@@ -74,6 +79,8 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     Tyr/Model/Qwen/Attention.lean:195-196.  `check_mode` runs the fp32-FMA kernel.
     `window_size` > 0 adds the causal sliding window of lean_torch_sdpa_gqa_window
     (cc/src/tyr.cpp:3986-3996): key j is visible to query i only if j <= i and i - j < window_size.
+    `key_mask` (uint8 / bool CUDA tensor [batch, kv_seq], 0 = padding key) hides padding keys
+    from every query, the key side of lean_torch_sdpa_gqa_mask (cc/src/tyr.cpp:4063-4086).
     Launcher convention of Examples/GPU/RunFlashAttn.lean:68-81: outputs may be
     pre-allocated by the caller and are written in place.
     """
@@ -87,7 +94,13 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous()
                             or tuple(lse.shape) != tuple(q.shape[:3])):
         raise ValueError("lse must be a contiguous float32 [batch, n_head, q_seq] tensor")
-    a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode, window_size)
+    if key_mask is not None:
+        if key_mask.dtype == torch.bool:
+            key_mask = key_mask.view(torch.uint8)
+        if (not key_mask.is_cuda or key_mask.dtype != torch.uint8 or key_mask.dim() != 2
+                or key_mask.stride(1) != 1 or tuple(key_mask.shape) != (k.shape[0], k.shape[2])):
+            raise ValueError("key_mask must be a uint8/bool CUDA tensor [batch, kv_seq]")
+    a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode, window_size, key_mask)
     with torch.cuda.device(q.device):
         check(_lib.load().tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
     return out, lse
@@ -133,6 +146,21 @@ def scaledDotProductAttentionGQAWindow(query, key, value, dropout_p: float = 0.0
     if query.shape[2] != key.shape[2]:
         raise ValueError("scaledDotProductAttentionGQAWindow needs q_seq == kv_seq")
     out, _ = attentionFwd(query, key, value, is_causal=True, return_lse=False, window_size=window_size)
+    return out
+
+
+def scaledDotProductAttentionGQAMask(query, key, value, attn_mask, dropout_p: float = 0.0,
+                                     is_causal: bool = True, enable_gqa: bool = False):
+    """Tyr/Torch.lean:1103-1118 -> lean_torch_sdpa_gqa_mask (cc/src/tyr.cpp:4024-4095).
+    attn_mask [batch, seq]: non-zero = valid key, 0 = padding (any numeric or bool dtype)."""
+    if dropout_p != 0.0:
+        raise AttnError(-6)
+    if not enable_gqa and query.shape[1] != key.shape[1]:
+        raise AttnError(-2)
+    if query.shape[2] != key.shape[2]:
+        raise ValueError("scaledDotProductAttentionGQAMask needs q_seq == kv_seq")
+    km = (attn_mask != 0).to(torch.uint8).contiguous()   # one byte per key for the C ABI
+    out, _ = attentionFwd(query, key, value, is_causal=is_causal, return_lse=False, key_mask=km)
     return out
 
 
