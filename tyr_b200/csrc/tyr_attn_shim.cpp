@@ -88,8 +88,11 @@ void* current_stream(const torch::Tensor& t) {
 //   usage inside lean_torch_sdpa_gqa (cc/src/tyr.cpp:3913-3949), before the
 //   repeat_interleave:   torch::Tensor out; if (tyr_b200_try_sdpa(q, k, v, dropout_p,
 //   is_causal, enable_gqa, &out)) return giveTensor(out);
+// `window_size` > 0: the sliding window of lean_torch_sdpa_gqa_window (cc/src/tyr.cpp:3953-4018).
+// `padding_mask` defined: the [batch, seq] key mask of lean_torch_sdpa_gqa_mask (4024-4095).
 bool tyr_b200_try_sdpa(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
-                       double dropout_p, bool is_causal, bool enable_gqa, torch::Tensor* out) {
+                       double dropout_p, bool is_causal, bool enable_gqa, torch::Tensor* out,
+                       uint64_t window_size = 0, const torch::Tensor& padding_mask = torch::Tensor()) {
   if (dropout_p != 0.0 || !eligible(q) || !eligible(k) || !eligible(v)) return false;
   if (!enable_gqa && q.size(1) != k.size(1)) return false;
   if (k.size(1) == 0 || q.size(1) % k.size(1) != 0) return false;
@@ -97,6 +100,16 @@ bool tyr_b200_try_sdpa(const torch::Tensor& q, const torch::Tensor& k, const tor
   torch::Tensor o = torch::empty(q.sizes(), q.options());  // allocation only
   TyrAttnPrefillArgs a;
   fill_args(a, q, k, v, o, nullptr, is_causal);
+  if (window_size > 0x7fffffffu) return false;
+  a.window_size = (int32_t)window_size;
+  torch::Tensor key_bytes;  // one byte per key, kept alive until the launch is queued
+  if (padding_mask.defined()) {
+    if (padding_mask.dim() != 2 || padding_mask.size(0) != k.size(0) || padding_mask.size(1) != k.size(2))
+      return false;
+    key_bytes = padding_mask.to(q.device()).ne(0).to(torch::kUInt8).contiguous();
+    a.key_mask = key_bytes.data_ptr<uint8_t>();
+    a.key_mask_stride = key_bytes.stride(0);
+  }
   if (tyr_b200_attn_prefill(&a, current_stream(q)) != 0) return false;
   *out = o;
   return true;
