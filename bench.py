@@ -252,6 +252,12 @@ def sharded_workloads(tnn, dev, rank, world, barrier, all_max, steps=10, warmup=
                                   steps, warmup, barrier) / steps)
         out[name] = {"ms": sec * 1e3, "tflops": w.flops / sec / 1e12, "shard_axis": sh.axis,
                      "shard": f"batch {nb} x kv_heads {nh} per GPU"}
+        if sh.axis in ("heads", "batch"):
+            # optional replicated output (only when a caller asks for it): one NCCL all-gather of
+            # the O shards into local staging + a local permute; reported apart from the kernel
+            gsec = all_max(time_events(lambda: P.gather_output(o, sh.axis), 5, 2, barrier) / 5)
+            out[name]["replicate_output_ms"] = gsec * 1e3
+            out[name]["replicate_output_gbs_per_gpu"] = o.numel() * 2 * (world - 1) / gsec / 1e9
         del q, k, v, o, lse
     w = W.WORKLOADS["qwen3_8b_decode"]
     lens = W.decode_lengths(w)
