@@ -123,6 +123,60 @@ def test_query_and_key_lengths_differ(Sq, Skv, causal):
     assert_parity(o, None, ro, None, (Sq, Skv, causal))
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(3, 1), (6, 2), (5, 5), (8, 1), (2, 2)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_gqa_group_sizes(Hq, Hkv, causal):
+    # even groups pair two heads of a KV head in one work item, odd groups pair row blocks
+    S, D = 330, 128
+    q, k, v = randn(2, Hq, S, D, seed=Hq), randn(2, Hkv, S, D, seed=Hq + 1), randn(2, Hkv, S, D, seed=Hq + 2)
+    o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=causal)
+    ro, rlse = oracle(q, k, v, causal)
+    assert_parity(o, lse, ro, rlse, (Hq, Hkv, causal))
+
+
+def test_random_shapes_against_the_fp32_kernel():
+    """Seeded sweep over shapes, masks and strides: tensor-core kernel vs the fp32-FMA kernel."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        D = int(rng.choice([64, 128]))
+        Hkv = int(rng.integers(1, 4))
+        g = int(rng.choice([1, 2, 3, 4]))
+        B = int(rng.integers(1, 4))
+        Sq = int(rng.integers(1, 900))
+        same = bool(rng.integers(0, 2))
+        Skv = Sq if same else int(rng.integers(1, 900))
+        causal = bool(rng.integers(0, 2))
+        window = int(rng.integers(1, 400)) if (same and rng.integers(0, 3) == 0) else 0
+        use_mask = same and not window and rng.integers(0, 4) == 0
+        q, k, v = randn(B, Hkv * g, Sq, D, seed=case), randn(B, Hkv, Skv, D, seed=case + 100), randn(B, Hkv, Skv, D, seed=case + 200)
+        km = None
+        if use_mask:
+            km = torch.tensor(rng.integers(0, 2, (B, Skv)), dtype=torch.uint8)
+            km[:, 0] = 1                      # every causal row keeps at least its first key
+            km = km.to(DEV)
+        kw = dict(is_causal=causal, window_size=window, key_mask=km)
+        o, lse = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), **kw)
+        oc, lc = tnn.attentionFwd(q.to(DEV), k.to(DEV), v.to(DEV), check_mode=True, **kw)
+        tag = (case, B, Hkv, g, Sq, Skv, D, causal, window, use_mask)
+        assert not torch.isnan(o.float()).any(), tag
+        assert (o.float() - oc.float()).abs().max().item() <= O_MAX_ABS, tag
+        assert ((lse - lc).abs() / lc.abs().clamp(min=1.0)).max().item() <= LSE_REL, tag
+
+
+def test_two_streams_do_not_interfere():
+    q, k, v = randn(2, 4, 600, 128, seed=81).to(DEV), randn(2, 2, 600, 128, seed=82).to(DEV), randn(2, 2, 600, 128, seed=83).to(DEV)
+    ref, ref_lse = tnn.attentionFwd(q, k, v, is_causal=True)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for st in (s1, s2, s1, s2):
+        with torch.cuda.stream(st):
+            outs.append(tnn.attentionFwd(q, k, v, is_causal=True))
+    torch.cuda.synchronize()
+    for o, l in outs:
+        assert torch.equal(o, ref) and torch.equal(l, ref_lse)
+
+
 def test_typed_calls_mirror_the_lean_externs():
     q, k, v = randn(2, 4, 200, 64, seed=7), randn(2, 4, 200, 64, seed=8), randn(2, 4, 200, 64, seed=9)
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
