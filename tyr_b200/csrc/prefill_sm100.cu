@@ -174,6 +174,9 @@ __device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
 template <int D>
 __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint64_t q_desc, uint64_t k_desc) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, false);
+  // Opaque to the optimizer: the per-step descriptors are recomputed at each use instead of
+  // being kept (and spilled) as loop invariants of the issuing thread.
+  asm volatile("" : "+l"(q_desc), "+l"(k_desc));
 #pragma unroll
   for (int kb = 0; kb < D / 64; ++kb) {
 #pragma unroll
@@ -189,6 +192,7 @@ template <int D>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc,
                                          bool accumulate, int half) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
+  asm volatile("" : "+l"(v_desc), "+r"(p_tmem));  // as in issue_qk
 #pragma unroll
   for (int k4 = 0; k4 < kBN / 32; ++k4) {
     const int kk = half * (kBN / 32) + k4;
@@ -414,7 +418,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int w = snake_item(it, total_items, p.snake);
       if (w < 0) break;
       const Item im = decode_item<kWindow>(w, p);
-      const int row = im.row[t] + r;  // query index
+      const int row = (t ? im.row[1] : im.row[0]) + r;  // query index
+      const int hq = t ? im.hq[1] : im.hq[0];
       const int n_t = t ? im.n1 : im.n0;
       float m_ref = -INFINITY, l = 0.f;
 
@@ -527,7 +532,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after();
       const float inv_l = 1.0f / l;
       const bool row_ok = row < p.q_seq;
-      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + im.hq[t] * p.o_stride_h + (int64_t)row * p.o_stride_s;
+      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -545,7 +550,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       if (p.lse != nullptr && row_ok)
-        p.lse[im.b * p.lse_stride_b + im.hq[t] * p.lse_stride_h + row] =
+        p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
       // O_t is read: order these loads before the next item's first PV_t, which this
       // warp gates through p_half
