@@ -171,34 +171,41 @@ __device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
 // The issuing thread shares its SM sub-partition with two softmax warps, so every
 // instruction it spends per MMA delays the tensor pipe: descriptors are built once per
 // tile and stage, and each MMA only adds a compile-time constant to the address field.
+constexpr uint32_t kDescHi = umma_desc_hi(1024);  // 8-row groups of every operand tile are 1024 B apart
+
 template <int D>
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint64_t q_desc, uint64_t k_desc) {
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, false);
   // Opaque to the optimizer: the per-step descriptors are recomputed at each use instead of
   // being kept (and spilled) as loop invariants of the issuing thread.
-  asm volatile("" : "+l"(q_desc), "+l"(k_desc));
+  asm volatile("" : "+r"(q_lo), "+r"(k_lo));
 #pragma unroll
   for (int kb = 0; kb < D / 64; ++kb) {
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      const uint64_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
-      umma_ss(s_tmem, q_desc + off, k_desc + off, idesc, (kb | ks) != 0);
+      const uint32_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
+      if (kb == 0 && ks == 0)
+        umma_ss_lo<0>(s_tmem, q_lo, k_lo, kDescHi, idesc, 0);
+      else
+        umma_ss_lo<1>(s_tmem, q_lo + off, k_lo + off, kDescHi, idesc, 1);
     }
   }
 }
 
 // `half` selects keys [64*half, 64*half + 64) of the tile.
 template <int D>
-__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc,
+__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_lo,
                                          bool accumulate, int half) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
-  asm volatile("" : "+l"(v_desc), "+r"(p_tmem));  // as in issue_qk
+  asm volatile("" : "+r"(v_lo), "+r"(p_tmem));  // as in issue_qk
 #pragma unroll
   for (int k4 = 0; k4 < kBN / 32; ++k4) {
     const int kk = half * (kBN / 32) + k4;
     // 16 keys = two 8-row groups of the V tile; 16 bf16 of P = 8 TMEM columns
-    umma_ts(o_tmem, p_tmem + kk * 8, v_desc + ((kk * 2048) >> 4), idesc,
-            (accumulate || kk != 0) ? 1u : 0u);
+    if (k4 == 0)
+      umma_ts_lo<-1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, accumulate ? 1u : 0u);
+    else
+      umma_ts_lo<1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, 1);
   }
 }
 
@@ -326,8 +333,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (lane == 0) {
         const uint32_t tS0 = tmem + C::kTmemS, tS1 = tS0 + kBN;
         const uint32_t tO0 = tmem + C::kTmemO, tO1 = tO0 + D;
-        const uint64_t q_desc0 = umma_smem_desc(sQ, 16, 1024);
-        const uint64_t q_desc1 = umma_smem_desc(sQ + C::kTileBytes, 16, 1024);
+        const uint32_t q_desc0 = umma_desc_lo(sQ, 16);
+        const uint32_t q_desc1 = umma_desc_lo(sQ + C::kTileBytes, 16);
         bool ok = true;
         int kc = 0, vc = 0;      // K / V tiles consumed so far
         int pc0 = 0, pc1 = 0;    // P tiles consumed so far, per Q tile
@@ -342,7 +349,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_after();
           {
             const int s = kc % C::kKStages;
-            const uint64_t k_desc = umma_smem_desc(sK + s * C::kTileBytes, 16, 1024);
+            const uint32_t k_desc = umma_desc_lo(sK + s * C::kTileBytes, 16);
             issue_qk<D>(tS0, q_desc0, k_desc);
             umma_commit(bar(B::s_full + 0));
             if (n0 == 1) umma_commit(bar(B::q_empty + 0));
@@ -359,8 +366,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
             if (ok && next) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
             if (!ok) break;
-            const uint64_t v_smem = umma_smem_desc(sV + vs * C::kTileBytes, C::kBoxBytes, 1024);
-            const uint64_t k_smem = umma_smem_desc(sK + ks * C::kTileBytes, 16, 1024);
+            const uint32_t v_smem = umma_desc_lo(sV + vs * C::kTileBytes, C::kBoxBytes);
+            const uint32_t k_smem = umma_desc_lo(sK + ks * C::kTileBytes, 16);
             if (j < n0) {
               ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
               if (!ok) break;
