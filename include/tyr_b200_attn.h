@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 3
+#define TYR_ATTN_ABI_VERSION 4
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -225,6 +225,55 @@ typedef struct TyrAttnPrologueArgs {
 } TyrAttnPrologueArgs;
 
 int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Backward of the prefill operator: dQ, dK, dV from dO, the forward inputs, the
+ * forward output O and the per-row LSE the forward returned.
+ * In the reference the gradient of the typed attention call comes from LibTorch
+ * autograd (`output.backward(grad_output)`, cc/src/tyr.cpp:2111-2122) differentiating
+ * the SDPA operator of cc/src/tyr.cpp:2563-2589 / 3910-3949; its own DSL statement of
+ * the same arithmetic is Tyr/GPU/Kernels/MhaH100.lean:196-344 (a preparation kernel
+ * d = rowsum(dO * O), then P = exp(scale*S - lse), dV = P^T dO, dP = dO V^T,
+ * dS = scale * P * (dP - d), dQ = dS K, dK = dS^T Q, with P and dS rounded to bf16
+ * before the matrix products).  This entry point follows that formulation:
+ *
+ *   delta[b,h,i] = sum_d dO[b,h,i,d] * O[b,h,i,d]
+ *   P[i,j]  = exp(scale * q_i.k_j - lse[i])        (0 where the causal mask hides j)
+ *   dV_j   += P[i,j] * dO_i     dP[i,j] = dO_i.v_j
+ *   dS[i,j] = scale * P[i,j] * (dP[i,j] - delta[i])
+ *   dQ_i   += dS[i,j] * k_j      dK_j   += dS[i,j] * q_i
+ * dK and dV of a KV head sum over the n_head / n_kv_head query heads that share it.
+ *
+ * Tensors are bf16 [batch, heads, seq, head_dim] with the stride rules of the prefill
+ * call (unit inner stride, 16-byte aligned rows); lse is fp32 contiguous
+ * [batch, n_head, q_seq] as written by tyr_b200_attn_prefill.  head_dim in {64,128}.
+ * `workspace` is caller-provided device memory of at least
+ * tyr_b200_attn_backward_workspace_bytes() bytes (fp32 row statistics); nothing is
+ * allocated by the call.  Three launches on `stream`: the row-statistics kernel, the
+ * dK/dV kernel, the dQ kernel.  No sliding window or key mask in this entry point.
+ * ---------------------------------------------------------------------- */
+typedef struct TyrAttnBackwardArgs {
+  const void* q;            /* [batch, n_head,    q_seq,  head_dim] */
+  const void* k;            /* [batch, n_kv_head, kv_seq, head_dim] */
+  const void* v;            /* [batch, n_kv_head, kv_seq, head_dim] */
+  const void* o;            /* forward output, [batch, n_head, q_seq, head_dim] */
+  const void* d_o;          /* gradient of the loss w.r.t. o, same layout rules */
+  const float* lse;         /* [batch, n_head, q_seq] fp32 from the forward */
+  void* d_q;                /* out, [batch, n_head,    q_seq,  head_dim] */
+  void* d_k;                /* out, [batch, n_kv_head, kv_seq, head_dim] */
+  void* d_v;                /* out, [batch, n_kv_head, kv_seq, head_dim] */
+  void* workspace;
+  uint64_t workspace_bytes;
+  int32_t batch, n_head, n_kv_head, q_seq, kv_seq, head_dim;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];   /* elements: batch, head, seq */
+  int32_t dtype;            /* TYR_ATTN_BF16 */
+  int32_t is_causal;        /* key j hidden from query i when j > i, as in the forward */
+  float scale;              /* <= 0: 1/sqrt(head_dim) */
+} TyrAttnBackwardArgs;
+
+uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, int32_t q_seq);
+int tyr_b200_attn_backward(const TyrAttnBackwardArgs* args, void* stream);
 
 /* ------------------------------------------------------------------------
  * Host-buffer call: same arithmetic as tyr_b200_attn_prefill, but every

@@ -23,6 +23,7 @@ EXPORTS = [
     "tyr_b200_sdpa_gqa_window", "tyr_b200_sdpa_gqa_mask",
     "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_decode_static",
     "tyr_b200_attn_merge", "tyr_b200_attn_qk_prologue",
+    "tyr_b200_attn_backward_workspace_bytes", "tyr_b200_attn_backward",
     "tyr_b200_attn_prefill_host", "tyr_b200_attn_device_status", "tyr_b200_attn_strerror",
     "tyr_b200_attn_abi_version", "tyr_b200_attn_launch_count",
 ]
@@ -57,6 +58,19 @@ class PrologueArgs(ctypes.Structure):
         ("x", vp), ("out", vp), ("norm_weight", vp), ("cos", vp), ("sin", vp), ("positions", vp),
         ("position0", c_i32), ("batch", c_i32), ("seq", c_i32), ("n_head", c_i32), ("head_dim", c_i32),
         ("x_stride", c_i64 * 3), ("out_stride", c_i64 * 3), ("eps", c_f32),
+    ]
+
+
+class BackwardArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", vp), ("k", vp), ("v", vp), ("o", vp), ("d_o", vp), ("lse", vp),
+        ("d_q", vp), ("d_k", vp), ("d_v", vp), ("workspace", vp), ("workspace_bytes", c_u64),
+        ("batch", c_i32), ("n_head", c_i32), ("n_kv_head", c_i32), ("q_seq", c_i32),
+        ("kv_seq", c_i32), ("head_dim", c_i32),
+        ("q_stride", c_i64 * 3), ("k_stride", c_i64 * 3), ("v_stride", c_i64 * 3),
+        ("o_stride", c_i64 * 3), ("do_stride", c_i64 * 3),
+        ("dq_stride", c_i64 * 3), ("dk_stride", c_i64 * 3), ("dv_stride", c_i64 * 3),
+        ("dtype", c_i32), ("is_causal", c_i32), ("scale", c_f32),
     ]
 
 
@@ -95,6 +109,10 @@ def load() -> ctypes.CDLL:
     L.tyr_b200_attn_decode_static.restype = ctypes.c_int
     L.tyr_b200_attn_qk_prologue.argtypes = [ctypes.POINTER(PrologueArgs), vp]
     L.tyr_b200_attn_qk_prologue.restype = ctypes.c_int
+    L.tyr_b200_attn_backward_workspace_bytes.argtypes = [c_i32] * 3
+    L.tyr_b200_attn_backward_workspace_bytes.restype = c_u64
+    L.tyr_b200_attn_backward.argtypes = [ctypes.POINTER(BackwardArgs), vp]
+    L.tyr_b200_attn_backward.restype = ctypes.c_int
     L.tyr_b200_attn_merge.argtypes = [vp] * 6 + [c_i64, c_i32, vp]
     L.tyr_b200_attn_merge.restype = ctypes.c_int
     L.tyr_b200_attn_device_status.argtypes = [c_i32, c_i32]

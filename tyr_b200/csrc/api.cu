@@ -236,6 +236,41 @@ int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* a, void* stream) {
   return launch_qk_prologue(*a, static_cast<cudaStream_t>(stream));
 }
 
+uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, int32_t q_seq) {
+  if (batch <= 0 || n_head <= 0 || q_seq <= 0) return 0;
+  return backward_workspace_bytes(batch, n_head, q_seq);
+}
+
+int tyr_b200_attn_backward(const TyrAttnBackwardArgs* a, void* stream) {
+  if (!a || !a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->d_q || !a->d_k || !a->d_v)
+    return -TYR_ATTN_ERR_NULL;
+  if (a->batch <= 0 || a->n_head <= 0 || a->n_kv_head <= 0 || a->q_seq <= 0 || a->kv_seq <= 0)
+    return -TYR_ATTN_ERR_SHAPE;
+  if (a->n_head % a->n_kv_head != 0) return -TYR_ATTN_ERR_SHAPE;
+  if (a->dtype != TYR_ATTN_BF16) return -TYR_ATTN_ERR_DTYPE;
+  if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
+  if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
+  const void* ptrs[8] = {a->q, a->k, a->v, a->o, a->d_o, a->d_q, a->d_k, a->d_v};
+  const int64_t* strides[8] = {a->q_stride, a->k_stride, a->v_stride, a->o_stride,
+                               a->do_stride, a->dq_stride, a->dk_stride, a->dv_stride};
+  for (int t = 0; t < 8; ++t) {
+    if (!aligned16(ptrs[t])) return -TYR_ATTN_ERR_ALIGN;
+    const bool kv = (t == 1 || t == 2 || t == 6 || t == 7);
+    const int dims[3] = {a->batch, kv ? a->n_kv_head : a->n_head, kv ? a->kv_seq : a->q_seq};
+    for (int i = 0; i < 3; ++i)
+      if (dims[i] > 1 && (strides[t][i] <= 0 || (strides[t][i] & 7))) return -TYR_ATTN_ERR_ALIGN;
+  }
+  if (!a->workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 15u) ||
+      a->workspace_bytes < backward_workspace_bytes(a->batch, a->n_head, a->q_seq))
+    return -TYR_ATTN_ERR_WORKSPACE;
+  int dev = 0, rc;
+  if ((rc = current_device_checked(&dev))) return rc;
+  DeviceState* ds = device_state(dev);
+  if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+  return launch_backward_sm100(*a, resolve_scale(a->scale, a->head_dim), ds->status,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   int rc = check_prefill(a);
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment

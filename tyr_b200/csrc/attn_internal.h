@@ -1,5 +1,6 @@
 // Internal launch interface shared by the .cu files of the attention library.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -17,6 +18,12 @@ void count_launch(int n = 1);
 
 // prefill_sm100.cu — tcgen05/TMA kernel, bf16, head_dim in {64,128}.
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st);
+// 128-byte-swizzled 64 x 128 box map over a bf16 [batch, heads, seq, d] tensor with element strides
+// {batch, head, seq}; encoded maps are cached per thread (prefill_sm100.cu).
+int make_tile_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d, const int64_t* stride);
+// backward_sm100.cu — tcgen05/TMA kernels, bf16, head_dim in {64,128}.
+size_t backward_workspace_bytes(int batch, int n_head, int q_seq);
+int launch_backward_sm100(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStream_t st);
 // check_fp32.cu — fp32-FMA kernel, bf16 or fp32 I/O, any head_dim <= 256.
 int launch_prefill_check(const TyrAttnPrefillArgs& a, float scale, cudaStream_t st);
 // decode_splitkv.cu

@@ -1,0 +1,520 @@
+// Attention backward for sm_100a: dQ, dK, dV from dO, Q, K, V, O and the forward's LSE.
+//
+// Arithmetic (the formulation of Tyr/GPU/Kernels/MhaH100.lean:196-344; in the reference's
+// models the same gradient comes from LibTorch autograd, cc/src/tyr.cpp:2111-2122):
+//   delta_i = sum_d dO_i,d O_i,d            P_ij = exp(scale q_i.k_j - lse_i)   (0 under the mask)
+//   dV_j += P_ij dO_i     dP_ij = dO_i.v_j   dS_ij = scale P_ij (dP_ij - delta_i)
+//   dQ_i += dS_ij k_j     dK_j += dS_ij q_i
+// with P and dS rounded to bf16 before the matrix products, fp32 accumulation.
+//
+// Three launches:
+//   bwd_rowstats_kernel : -lse*log2(e) and -delta*scale per query row, padded to whole tiles
+//                         (padding rows get -inf / 0, so they produce P = 0 downstream).
+//   bwd_kernel<D, 0>    : one CTA per 128 keys of a (batch, KV head).  K and V tiles stay in
+//                         shared memory; the Q and dO tiles of every query head of the group and
+//                         every query block the keys are visible to stream through a 2-stage TMA
+//                         ring.  Transposed orientation (rows = keys): S^T = K Q^T, dP^T = V dO^T
+//                         by tcgen05.mma from shared memory into tensor memory, P^T and dS^T go
+//                         back to tensor memory as bf16 and feed dV += P^T dO, dK += dS^T Q as the
+//                         A operand.  dK and dV accumulate in tensor memory over the whole group:
+//                         no atomics, a deterministic sum.
+//   bwd_kernel<D, 1>    : one CTA per 128 query rows of a (batch, query head).  Q and dO stay,
+//                         K and V stream; S = Q K^T, dP = dO V^T, dS to tensor memory, dQ += dS K.
+// Both instantiations are the same program: a resident tile pair, a streamed tile pair, two
+// score-shaped products, an elementwise step by four warps (thread = row = TMEM lane), then one
+// or two accumulating products whose B operand is a streamed tile read MN-major.
+// Tensor memory (512 columns): S [0,128) dP [128,256) acc1 [256,256+D) acc2 [256+D,256+2D);
+// bf16 P / dS overwrite the first 64 columns of S / dP once those are in registers.
+// Warps: 0 TMA producer, 1 MMA issuer, 2 TMEM allocation, 4-7 elementwise + epilogue.
+// Every wait is bounded and reports through the per-device status word, as in the forward.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+
+#include "attn_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace tyr {
+namespace {
+
+constexpr int kT = 128;           // tile rows and score-tile columns
+constexpr int kBwdThreads = 256;  // 8 warps
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BCfg {
+  static constexpr int kBoxes = D / 64;                // 128-byte boxes per row
+  static constexpr uint32_t kBoxBytes = 128u * 128u;   // 128 rows x 128 B
+  static constexpr uint32_t kTileBytes = kBoxes * kBoxBytes;
+  static constexpr int kStages = 2;
+  static constexpr uint32_t kRes1 = 0, kRes2 = kTileBytes;
+  static constexpr uint32_t kStr = 2 * kTileBytes;     // stage s: tile 1 at kStr + 2 s T, tile 2 one T further
+  static constexpr uint32_t kBarOff = kStr + kStages * 2 * kTileBytes;
+  // barriers
+  static constexpr int res_full = 0;                   // resident pair landed
+  static constexpr int str_full = 1;                   // [2] streamed pair landed
+  static constexpr int str_empty = 3;                  // [2] accumulating products have read the pair
+  static constexpr int s_full = 5;                     // S and dP in tensor memory
+  static constexpr int p_full = 6;                     // P / dS written (one arrival per elementwise warp)
+  static constexpr int acc_full = 7;                   // last accumulating product done
+  static constexpr int kNumBars = 8;
+  static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc1 = 256, kTmemAcc2 = 256 + D;
+  static_assert(256 + 2 * D <= 512, "tensor memory budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+struct BwdParams {
+  __nv_bfloat16* out1;  // mode 0: dK, mode 1: dQ
+  __nv_bfloat16* out2;  // mode 0: dV
+  int64_t out1_stride[3], out2_stride[3];
+  const float* neg_lse2;     // [batch * n_head, sq_pad]  -lse * log2(e); -inf on padding rows
+  const float* neg_delta_s;  // [batch * n_head, sq_pad]  -delta * scale;  0 on padding rows
+  int sq_pad;
+  int batch, q_seq, kv_seq, n_head, n_kv_head, group, causal;
+  int n_qblk, n_kblk;
+  float sl2, scale;
+  int* status;
+};
+
+constexpr uint32_t kBwdDescHi = umma_desc_hi(1024);
+
+// score-shaped product: D[128 x 128] = A[128 x D] B[128 x D]^T, both K-major in shared memory
+template <int D>
+__device__ __forceinline__ void issue_nt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+  constexpr uint32_t idesc = umma_idesc_bf16(kT, kT, false);
+  asm volatile("" : "+r"(a_lo), "+r"(b_lo));  // recomputed per use: keeps the issuer's registers few
+#pragma unroll
+  for (int kb = 0; kb < D / 64; ++kb) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const uint32_t off = (kb * BCfg<D>::kBoxBytes + ks * 32) >> 4;
+      if (kb == 0 && ks == 0)
+        umma_ss_lo<0>(d_tmem, a_lo, b_lo, kBwdDescHi, idesc, 0);
+      else
+        umma_ss_lo<1>(d_tmem, a_lo + off, b_lo + off, kBwdDescHi, idesc, 1);
+    }
+  }
+}
+// accumulating product: D[128 x D] (+)= A[128 x 128 bf16, tensor memory] B[128 x D], B MN-major
+template <int D>
+__device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc_bf16(kT, D, true);
+  asm volatile("" : "+r"(b_lo), "+r"(a_tmem));
+#pragma unroll
+  for (int kk = 0; kk < kT / 16; ++kk) {
+    // 16 rows of B = two 8-row groups of the tile; 16 bf16 of A = 8 TMEM columns
+    if (kk == 0)
+      umma_ts_lo<-1>(d_tmem, a_tmem, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u);
+    else
+      umma_ts_lo<1>(d_tmem, a_tmem + kk * 8, b_lo + ((kk * 2048) >> 4), kBwdDescHi, idesc, 1);
+  }
+}
+
+// kMode 0: rows = keys, resident (K, V), streamed (Q, dO), out1 = dK, out2 = dV.
+// kMode 1: rows = queries, resident (Q, dO), streamed (K, V), out1 = dQ.
+template <int D, int kMode>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ CUtensorMap tm_res2,
+           const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
+           const BwdParams p) {
+  using C = BCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
+  const uint32_t sBar = base + C::kBarOff;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work unit of this CTA; the heaviest units (most streamed tiles under a causal mask) come first
+  int blk, head, b;
+  {
+    const int n_blk = kMode == 0 ? p.n_kblk : p.n_qblk;
+    const int heads = kMode == 0 ? p.n_kv_head : p.n_head;
+    const int lvl = blockIdx.x / (heads * p.batch);
+    const int rem = blockIdx.x - lvl * heads * p.batch;
+    head = rem % heads;
+    b = rem / heads;
+    blk = kMode == 0 ? lvl : n_blk - 1 - lvl;
+  }
+  const int row0 = blk * kT;  // first key (mode 0) / query (mode 1) of the resident tiles
+  // streamed tiles: mode 0: query blocks [lo, n_qblk) of each of `group` query heads;
+  //                 mode 1: key blocks [0, hi]
+  int lo = 0, per_head, n_iter;
+  if (kMode == 0) {
+    lo = p.causal ? min(blk, p.n_qblk) : 0;  // first query block with a row >= the first key
+    per_head = p.n_qblk - lo;
+    n_iter = per_head * p.group;
+  } else {
+    per_head = p.causal ? min(p.n_kblk, blk + 1) : p.n_kblk;
+    n_iter = per_head;
+  }
+  const int res_head = head;
+  auto str_head = [&](int i) { return kMode == 0 ? head * p.group + i / per_head : head / p.group; };
+  auto str_blk = [&](int i) { return kMode == 0 ? lo + i % per_head : i; };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), i == C::p_full ? 4u : 1u);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_res1);
+    tma_prefetch_desc(&tm_res2);
+    tma_prefetch_desc(&tm_str1);
+    tma_prefetch_desc(&tm_str2);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
+#pragma unroll
+      for (int kb = 0; kb < C::kBoxes; ++kb) {
+        tma_load_4d(base + C::kRes1 + kb * C::kBoxBytes, &tm_res1, bar(C::res_full), kb * 64, row0, res_head, b);
+        tma_load_4d(base + C::kRes2 + kb * C::kBoxBytes, &tm_res2, bar(C::res_full), kb * 64, row0, res_head, b);
+      }
+      bool ok = true;
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int s = i % C::kStages;
+        if (i >= C::kStages) ok = mbar_wait(bar(C::str_empty + s), ((i / C::kStages) - 1) & 1, abortp);
+        if (!ok) break;
+        const uint32_t dst = base + C::kStr + s * 2 * C::kTileBytes;
+        mbar_expect_tx(bar(C::str_full + s), 2 * C::kTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < C::kBoxes; ++kb) {
+          tma_load_4d(dst + kb * C::kBoxBytes, &tm_str1, bar(C::str_full + s), kb * 64, str_blk(i) * kT,
+                      str_head(i), b);
+          tma_load_4d(dst + C::kTileBytes + kb * C::kBoxBytes, &tm_str2, bar(C::str_full + s), kb * 64,
+                      str_blk(i) * kT, str_head(i), b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_iter > 0) {
+      const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP;
+      const uint32_t tA1 = tmem + C::kTmemAcc1, tA2 = tmem + C::kTmemAcc2;
+      const uint32_t res1_lo = umma_desc_lo(base + C::kRes1, 16), res2_lo = umma_desc_lo(base + C::kRes2, 16);
+      auto scores = [&](int i) {  // S = res1 str1^T, dP = res2 str2^T
+        const int s = i % C::kStages;
+        const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
+        if (!mbar_wait(bar(C::str_full + s), (i / C::kStages) & 1, abortp)) return false;
+        tc_fence_after();
+        issue_nt<D>(tS, res1_lo, umma_desc_lo(t1, 16));
+        issue_nt<D>(tDP, res2_lo, umma_desc_lo(t1 + C::kTileBytes, 16));
+        umma_commit(bar(C::s_full));
+        return true;
+      };
+      bool ok = mbar_wait(bar(C::res_full), 0, abortp);
+      if (ok) ok = scores(0);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
+        ok = mbar_wait(bar(C::p_full), i & 1, abortp);
+        if (!ok) break;
+        tc_fence_after();
+        // dS (bf16, over the first columns of dP) times the first streamed tile, MN-major
+        issue_acc<D>(tA1, tDP, umma_desc_lo(t1, C::kBoxBytes), i > 0);
+        if (kMode == 0) issue_acc<D>(tA2, tS, umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes), i > 0);
+        umma_commit(bar(C::str_empty + s));
+        if (i + 1 < n_iter) ok = scores(i + 1);
+        else umma_commit(bar(C::acc_full));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------ elementwise + epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // row of the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
+    const uint64_t sl2x2 = pack_f32x2(p.sl2, p.sl2), scale2 = pack_f32x2(p.scale, p.scale);
+    bool ok = true;
+    // mode 1: this thread's row statistics
+    float nl_row = 0.f, nd_row = 0.f;
+    if (kMode == 1) {
+      const int64_t at = ((int64_t)b * p.n_head + head) * p.sq_pad + row0 + r;
+      nl_row = p.neg_lse2[at];
+      nd_row = p.neg_delta_s[at];
+    }
+    for (int i = 0; i < n_iter; ++i) {
+      ok = mbar_wait(bar(C::s_full), i & 1, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int col0 = str_blk(i) * kT;  // first query (mode 0) / key (mode 1) of the score columns
+      // columns this row keeps under the causal mask: mode 0 (row = key): query >= key;
+      // mode 1 (row = query): key <= query
+      int c_first = 0, c_limit = kT;
+      if (p.causal) {
+        if (kMode == 0) c_first = row0 + r - col0;
+        else c_limit = row0 + r - col0 + 1;
+      }
+      const bool masked = __any_sync(0xffffffffu, c_first > 0 || c_limit < kT);
+      const float* nl_col = nullptr;
+      const float* nd_col = nullptr;
+      if (kMode == 0) {
+        const int64_t at = ((int64_t)b * p.n_head + str_head(i)) * p.sq_pad + col0;
+        nl_col = p.neg_lse2 + at;
+        nd_col = p.neg_delta_s + at;
+      }
+#pragma unroll
+      for (int c = 0; c < kT / 32; ++c) {
+        uint32_t sr[32], dp[32];
+        tmem_ld32(tS + c * 32, sr);
+        tmem_ld32(tDP + c * 32, dp);
+        tmem_wait_ld();
+        tmem_ld_ready(sr);
+        tmem_ld_ready(dp);
+        if (masked) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (c * 32 + x < c_first || c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
+        }
+        uint32_t pk_p[16], pk_s[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          uint64_t nl2, nd2;
+          if (kMode == 0) {
+            // statistics of the two query columns (every lane reads the same addresses)
+            const float2 a = *reinterpret_cast<const float2*>(nl_col + c * 32 + 2 * x);
+            const float2 d = *reinterpret_cast<const float2*>(nd_col + c * 32 + 2 * x);
+            nl2 = pack_f32x2(a.x, a.y);
+            nd2 = pack_f32x2(d.x, d.y);
+          } else {
+            nl2 = pack_f32x2(nl_row, nl_row);
+            nd2 = pack_f32x2(nd_row, nd_row);
+          }
+          const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, nl2);
+          float t0, t1;
+          unpack_f32x2(t2, t0, t1);
+          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+          const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, nd2);
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
+          pk_p[x] = pack_bf16x2(p0, p1);
+          pk_s[x] = pack_bf16x2(d0, d1);
+        }
+        if (kMode == 0) tmem_st16(tS + c * 16, pk_p);
+        tmem_st16(tDP + c * 16, pk_s);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::p_full));
+    }
+
+    // epilogue: accumulators -> bf16 -> global, one row per thread
+    if (ok && n_iter > 0) {
+      ok = mbar_wait(bar(C::acc_full), 0, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int row = row0 + r;
+      const bool row_ok = row < (kMode == 0 ? p.kv_seq : p.q_seq);
+#pragma unroll
+      for (int which = 0; which < (kMode == 0 ? 2 : 1); ++which) {
+        const uint32_t tA = tmem + lane_addr + (which ? C::kTmemAcc2 : C::kTmemAcc1);
+        const int64_t* st = which ? p.out2_stride : p.out1_stride;
+        __nv_bfloat16* orow = (which ? p.out2 : p.out1) + b * st[0] + head * st[1] + (int64_t)row * st[2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (n_iter > 0) {
+            tmem_ld32(tA + c * 32, o);
+            tmem_wait_ld();
+            tmem_ld_ready(o);
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) o[x] = 0u;  // keys no query sees: zero gradient
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 wv;
+            wv.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]), __uint_as_float(o[q4 * 8 + 1]));
+            wv.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]));
+            wv.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]));
+            wv.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]));
+            if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = wv;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  // ------------------------------------------------------------------ exit
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    // Some wait gave up.  Give this CTA's outstanding TMA loads a bounded time
+    // to land before the shared memory goes away, then report.
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) {
+      }
+      atomicOr(p.status, abort_flag);
+    }
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+// Row statistics of the backward: one group of D/8 lanes per query row, 16-byte loads.
+template <int D>
+__global__ void __launch_bounds__(256)
+bwd_rowstats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                    const float* __restrict__ lse, float* __restrict__ neg_lse2,
+                    float* __restrict__ neg_delta_s, int n_head, int q_seq, int sq_pad, int64_t os_b,
+                    int64_t os_h, int64_t os_s, int64_t ds_b, int64_t ds_h, int64_t ds_s, float scale,
+                    int64_t total_rows) {
+  constexpr int kLanes = D / 8;  // lanes per row
+  const int64_t slot = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / kLanes;  // padded row index
+  const int sub = threadIdx.x % kLanes;
+  if (slot >= total_rows) return;
+  const int i = (int)(slot % sq_pad);
+  const int64_t bh = slot / sq_pad;
+  const int h = (int)(bh % n_head);
+  const int64_t b = bh / n_head;
+  float acc = 0.f;
+  if (i < q_seq) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * os_b + h * os_h + (int64_t)i * os_s + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * ds_b + h * ds_h + (int64_t)i * ds_s + sub * 8);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float2 af = __bfloat1622float2(a2[x]), gf = __bfloat1622float2(g2[x]);
+      acc = fmaf(af.x, gf.x, acc);
+      acc = fmaf(af.y, gf.y, acc);
+    }
+  }
+#pragma unroll
+  for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off, kLanes);
+  if (sub == 0) {
+    const bool real = i < q_seq;
+    neg_lse2[slot] = real ? -lse[(b * n_head + h) * (int64_t)q_seq + i] * kLog2e : -INFINITY;
+    neg_delta_s[slot] = real ? -acc * scale : 0.f;
+  }
+}
+
+template <int D, int kMode>
+int set_smem_attr() {
+  static std::atomic<bool> attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(bwd_kernel<D, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)BCfg<D>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev].store(true, std::memory_order_release);
+  }
+  return 0;
+}
+
+template <int D>
+int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStream_t st) {
+  using C = BCfg<D>;
+  const int n_qblk = (a.q_seq + kT - 1) / kT, n_kblk = (a.kv_seq + kT - 1) / kT;
+  const int sq_pad = n_qblk * kT;
+  const int64_t padded_rows = (int64_t)a.batch * a.n_head * sq_pad;
+  float* neg_lse2 = static_cast<float*>(a.workspace);
+  float* neg_delta_s = neg_lse2 + padded_rows;
+
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tile_map(&tq, a.q, a.batch, a.n_head, a.q_seq, D, a.q_stride))) return rc;
+  if ((rc = make_tile_map(&tk, a.k, a.batch, a.n_kv_head, a.kv_seq, D, a.k_stride))) return rc;
+  if ((rc = make_tile_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
+  if ((rc = make_tile_map(&tdo, a.d_o, a.batch, a.n_head, a.q_seq, D, a.do_stride))) return rc;
+  if ((rc = set_smem_attr<D, 0>())) return rc;
+  if ((rc = set_smem_attr<D, 1>())) return rc;
+
+  {
+    constexpr int kLanes = D / 8;
+    const int64_t threads = padded_rows * kLanes;
+    const int64_t blocks = (threads + 255) / 256;
+    if (blocks > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
+    bwd_rowstats_kernel<D><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(a.o), static_cast<const __nv_bfloat16*>(a.d_o), a.lse, neg_lse2,
+        neg_delta_s, a.n_head, a.q_seq, sq_pad, a.o_stride[0], a.o_stride[1], a.o_stride[2], a.do_stride[0],
+        a.do_stride[1], a.do_stride[2], scale, padded_rows);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+
+  BwdParams p;
+  p.neg_lse2 = neg_lse2;
+  p.neg_delta_s = neg_delta_s;
+  p.sq_pad = sq_pad;
+  p.batch = a.batch;
+  p.q_seq = a.q_seq;
+  p.kv_seq = a.kv_seq;
+  p.n_head = a.n_head;
+  p.n_kv_head = a.n_kv_head;
+  p.group = a.n_head / a.n_kv_head;
+  p.causal = a.is_causal ? 1 : 0;
+  p.n_qblk = n_qblk;
+  p.n_kblk = n_kblk;
+  p.scale = scale;
+  p.sl2 = scale * kLog2e;
+  p.status = status;
+
+  const long long grid_kv = (long long)n_kblk * a.n_kv_head * a.batch;
+  const long long grid_q = (long long)n_qblk * a.n_head * a.batch;
+  if (grid_kv > 0x7fffffffLL || grid_q > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
+
+  p.out1 = static_cast<__nv_bfloat16*>(a.d_k);
+  p.out2 = static_cast<__nv_bfloat16*>(a.d_v);
+  for (int i = 0; i < 3; ++i) {
+    p.out1_stride[i] = a.dk_stride[i];
+    p.out2_stride[i] = a.dv_stride[i];
+  }
+  bwd_kernel<D, 0><<<(unsigned)grid_kv, kBwdThreads, C::kSmemBytes, st>>>(tk, tv, tq, tdo, p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+
+  p.out1 = static_cast<__nv_bfloat16*>(a.d_q);
+  p.out2 = nullptr;
+  for (int i = 0; i < 3; ++i) {
+    p.out1_stride[i] = a.dq_stride[i];
+    p.out2_stride[i] = 0;
+  }
+  bwd_kernel<D, 1><<<(unsigned)grid_q, kBwdThreads, C::kSmemBytes, st>>>(tq, tdo, tk, tv, p);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+size_t backward_workspace_bytes(int batch, int n_head, int q_seq) {
+  const int64_t sq_pad = (int64_t)((q_seq + kT - 1) / kT) * kT;
+  return (size_t)(2 * (int64_t)batch * n_head * sq_pad * (int64_t)sizeof(float));
+}
+
+int launch_backward_sm100(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStream_t st) {
+  if (a.head_dim == 128) return launch_bwd<128>(a, scale, status, st);
+  if (a.head_dim == 64) return launch_bwd<64>(a, scale, status, st);
+  return -TYR_ATTN_ERR_HEAD_DIM;
+}
+
+}  // namespace tyr

@@ -745,6 +745,10 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 
 }  // namespace
 
+int make_tile_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d, const int64_t* stride) {
+  return make_map(m, ptr, batch, heads, seq, d, stride);
+}
+
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   const bool win = a.window_size > 0 || a.key_mask != nullptr;
   if (a.head_dim == 128) return win ? launch<128, 0, true>(a, scale, status, st) : launch<128, 0, false>(a, scale, status, st);

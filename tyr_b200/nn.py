@@ -20,7 +20,7 @@ from typing import Optional, Sequence, Tuple
 import torch
 
 from . import _lib
-from ._lib import AttnError, DecodeArgs, PrefillArgs, PrologueArgs, check
+from ._lib import AttnError, BackwardArgs, DecodeArgs, PrefillArgs, PrologueArgs, check
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -104,6 +104,49 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     with torch.cuda.device(q.device):
         check(_lib.load().tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
     return out, lse
+
+
+def attentionBwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                 d_o: torch.Tensor, is_causal: bool = True, scale: Optional[float] = None,
+                 workspace: Optional[torch.Tensor] = None
+                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """dQ, dK, dV of `attentionFwd` from dO, the forward's inputs, its output and its LSE.
+
+    The gradient LibTorch autograd produces for the typed attention call in the reference
+    (`autograd.backward`, Tyr/Torch.lean:742 -> cc/src/tyr.cpp:2111-2122), computed with the
+    formulation of Tyr/GPU/Kernels/MhaH100.lean:196-344.  dK and dV of a KV head are summed over
+    the query heads that share it.  `workspace` may be a caller-kept float32 CUDA tensor of at
+    least `backward_workspace_bytes(...) / 4` elements; one is allocated otherwise.
+    """
+    _require_cuda(q, k, v, o, d_o, lse)
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if (v.shape != k.shape or Bk != B or Dk != D or o.shape != q.shape or d_o.shape != q.shape
+            or tuple(lse.shape) != (B, Hq, Sq)):
+        raise ValueError("shape mismatch among q, k, v, o, d_o, lse")
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v, o, d_o)):
+        raise ValueError("q, k, v, o, d_o must be bfloat16")
+    if lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise ValueError("lse must be a contiguous float32 [batch, n_head, q_seq] tensor")
+    L = _lib.load()
+    need = int(L.tyr_b200_attn_backward_workspace_bytes(B, Hq, Sq))
+    if workspace is None:
+        workspace = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+    if workspace.dtype != torch.float32 or not workspace.is_contiguous() or workspace.numel() * 4 < need:
+        raise ValueError("workspace must be a contiguous float32 CUDA tensor of the required size")
+    d_q, d_k, d_v = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    a = BackwardArgs()
+    a.q, a.k, a.v, a.o, a.d_o, a.lse = (t.data_ptr() for t in (q, k, v, o, d_o, lse))
+    a.d_q, a.d_k, a.d_v = d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr()
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = B, Hq, Hkv, Sq, Skv, D
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", o), ("do_stride", d_o),
+                    ("dq_stride", d_q), ("dk_stride", d_k), ("dv_stride", d_v)):
+        getattr(a, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
+    a.dtype, a.is_causal, a.scale = _lib.TYR_ATTN_BF16, int(bool(is_causal)), float(scale or 0.0)
+    with torch.cuda.device(q.device):
+        check(L.tyr_b200_attn_backward(ctypes.byref(a), _stream_ptr(q)))
+    return d_q, d_k, d_v
 
 
 def _sdpa(q, k, v, dropout_p, is_causal, enable_gqa):
