@@ -204,6 +204,24 @@ def other_workloads(tnn, dev, peaks, steps=10, warmup=3):
                      "frac_tensor_peak": w.flops / sec / 1e12 / peaks["bf16_tflops"],
                      "frac_hbm_peak": w.io_bytes / sec / 1e9 / peaks["hbm_gbs"]}
         del q, k, v, o, lse
+    # backward of the headline and of the long-sequence workload: row statistics + dK/dV + dQ
+    # kernels; FLOPs by the usual convention of five score-sized products (2.5 x the forward)
+    for name in ("qwen3_0p6b_prefill", "qwen3_8b_prefill"):
+        w = W.WORKLOADS[name]
+        g = torch.Generator(device=dev).manual_seed(w.seed)
+        q = torch.randn(w.batch, w.n_head, w.seq, w.head_dim, device=dev, generator=g).bfloat16()
+        k = torch.randn(w.batch, w.n_kv_head, w.seq, w.head_dim, device=dev, generator=g).bfloat16()
+        v = torch.randn(w.batch, w.n_kv_head, w.seq, w.head_dim, device=dev, generator=g).bfloat16()
+        d_o = torch.randn(w.batch, w.n_head, w.seq, w.head_dim, device=dev, generator=g).bfloat16()
+        o, lse = tnn.attentionFwd(q, k, v, is_causal=w.causal)
+        ws = torch.empty(2 * lse.numel(), device=dev)
+        sec = time_events(lambda: tnn.attentionBwd(q, k, v, o, lse, d_o, is_causal=w.causal, workspace=ws),
+                          steps, warmup, lambda: None) / steps
+        out[name.replace("prefill", "backward")] = {
+            "ms": sec * 1e3, "tflops": 2.5 * w.flops / sec / 1e12,
+            "frac_tensor_peak": 2.5 * w.flops / sec / 1e12 / peaks["bf16_tflops"],
+            "note": "7 score-sized products are executed (S and dP are recomputed by the dQ kernel); 5 are counted"}
+        del q, k, v, d_o, o, lse, ws
     w = W.WORKLOADS["qwen3_8b_decode"]
     q, ks, vs, lens = W.make_decode(w, device=str(dev))
     q = q.to(dev)

@@ -71,6 +71,16 @@ def sdpa_gqa_mask(q, k, v, padding_mask, dropout_p: float = 0.0, is_causal: bool
     return F.scaled_dot_product_attention(q, k, v, mask, dropout_p, False)
 
 
+def sdpa_gqa_backward(q, k, v, d_o, is_causal: bool = True):
+    """Gradients LibTorch autograd gives the reference for its typed attention call:
+    `output.backward(grad_output)` (cc/src/tyr.cpp:2111-2122) through lean_torch_sdpa_gqa
+    (cc/src/tyr.cpp:3913-3949, repeat_interleave included).  Returns (d_q, d_k, d_v)."""
+    q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    out = sdpa_gqa(q, k, v, 0.0, is_causal, True)
+    out.backward(d_o)
+    return q.grad, k.grad, v.grad
+
+
 def lse(q, k, v, is_causal: bool):
     """Natural-log LSE of the scaled scores, [B,Hq,Sq] fp32, from ATen's CPU flash kernel."""
     n_head, n_kv_head = q.shape[1], k.shape[1]

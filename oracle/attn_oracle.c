@@ -24,6 +24,11 @@
  *                          (cc/src/tyr.cpp:4024-4095).
  *   tyr_oracle_sdpa_online the running max / running sum form of
  *                          Tyr/GPU/Codegen/Macros.lean:121-163 with fp32 state.
+ *   tyr_oracle_sdpa_backward  gradients of the direct form with respect to Q, K and V for a given dO,
+ *                          the derivative LibTorch autograd supplies to the reference
+ *                          (cc/src/tyr.cpp:2111-2122), written as in
+ *                          Tyr/GPU/Kernels/MhaH100.lean:196-344: d = rowsum(dO*O),
+ *                          dV = P^T dO, dP = dO V^T, dS = scale * P * (dP - d), dQ = dS K, dK = dS^T Q.
  *   tyr_oracle_merge2      LSE merge of two partial results,
  *                          Tyr/GPU/Kernels/RingAttn.lean:164-180.
  *   tyr_oracle_bf16_round  round-to-nearest-even fp32 -> bf16 -> fp32, the quantisation the
@@ -197,6 +202,91 @@ int tyr_oracle_sdpa_online(const float* q, const float* k, const float* v, float
     if (lse) lse[r] = logf(row_sum) + row_max;
   }
   return 0;
+}
+
+/* Backward of the direct form in double precision.  One (batch, KV head) per task: dK and dV
+ * of a KV head sum over the Hq / Hkv query heads that share it (the derivative of
+ * repeat_interleave, cc/src/tyr.cpp:3931-3938).  Returns 0, or -1 on bad arguments. */
+int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, const float* d_o,
+                             float* d_q, float* d_k, float* d_v, int B, int Hq, int Hkv, int Sq,
+                             int Skv, int D, int is_causal, float scale) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0) return -1;
+  const int g = Hq / Hkv;
+  const int64_t tasks = (int64_t)B * Hkv;
+  int failed = 0;
+#pragma omp parallel
+  {
+    double* p = (double*)malloc(sizeof(double) * (size_t)Skv);
+    double* dp = (double*)malloc(sizeof(double) * (size_t)Skv);
+    double* o = (double*)malloc(sizeof(double) * (size_t)D);
+    double* dk = (double*)malloc(sizeof(double) * (size_t)Skv * D);
+    double* dv = (double*)malloc(sizeof(double) * (size_t)Skv * D);
+    double* dq = (double*)malloc(sizeof(double) * (size_t)D);
+    if (!p || !dp || !o || !dk || !dv || !dq) {
+#pragma omp atomic write
+      failed = 1;
+    } else {
+#pragma omp for schedule(dynamic, 1)
+      for (int64_t t = 0; t < tasks; ++t) {
+        const int b = (int)(t / Hkv), hk = (int)(t % Hkv);
+        const float* kb = k + t * (int64_t)Skv * D;
+        const float* vb = v + t * (int64_t)Skv * D;
+        for (int64_t x = 0; x < (int64_t)Skv * D; ++x) dk[x] = dv[x] = 0.0;
+        for (int hh = 0; hh < g; ++hh) {
+          const int h = hk * g + hh;
+          for (int i = 0; i < Sq; ++i) {
+            const int64_t r = ((int64_t)b * Hq + h) * Sq + i;
+            const float* qr = q + r * D;
+            const float* gr = d_o + r * D;
+            const int n = is_causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv; /* keys j <= i */
+            double mx = -INFINITY, sum = 0.0, delta = 0.0;
+            for (int j = 0; j < n; ++j) {
+              double dot = 0.0;
+              for (int d = 0; d < D; ++d) dot += (double)qr[d] * (double)kb[(int64_t)j * D + d];
+              p[j] = dot * (double)scale;
+              if (p[j] > mx) mx = p[j];
+            }
+            for (int j = 0; j < n; ++j) {
+              p[j] = exp(p[j] - mx);
+              sum += p[j];
+            }
+            for (int d = 0; d < D; ++d) o[d] = 0.0;
+            for (int j = 0; j < n; ++j) {
+              p[j] /= sum; /* softmax row */
+              double g_dot_v = 0.0;
+              for (int d = 0; d < D; ++d) {
+                o[d] += p[j] * (double)vb[(int64_t)j * D + d];
+                g_dot_v += (double)gr[d] * (double)vb[(int64_t)j * D + d];
+              }
+              dp[j] = g_dot_v; /* dP = dO V^T */
+            }
+            for (int d = 0; d < D; ++d) delta += (double)gr[d] * o[d]; /* d = rowsum(dO * O) */
+            for (int d = 0; d < D; ++d) dq[d] = 0.0;
+            for (int j = 0; j < n; ++j) {
+              const double ds = (double)scale * p[j] * (dp[j] - delta);
+              for (int d = 0; d < D; ++d) {
+                dv[(int64_t)j * D + d] += p[j] * (double)gr[d];         /* dV = P^T dO */
+                dq[d] += ds * (double)kb[(int64_t)j * D + d];           /* dQ = dS K */
+                dk[(int64_t)j * D + d] += ds * (double)qr[d];           /* dK = dS^T Q */
+              }
+            }
+            for (int d = 0; d < D; ++d) d_q[r * D + d] = (float)dq[d];
+          }
+        }
+        for (int64_t x = 0; x < (int64_t)Skv * D; ++x) {
+          d_k[t * (int64_t)Skv * D + x] = (float)dk[x];
+          d_v[t * (int64_t)Skv * D + x] = (float)dv[x];
+        }
+      }
+    }
+    free(p);
+    free(dp);
+    free(o);
+    free(dk);
+    free(dv);
+    free(dq);
+  }
+  return failed ? -1 : 0;
 }
 
 /* L = Lr + log(1 + exp(Lb - Lr));  O = Or*exp(Lr - L) + Ob*exp(Lb - L)

@@ -35,6 +35,8 @@ def lib() -> ctypes.CDLL:
             [f32p, f32p, f32p, f32p, f32p] + [ctypes.c_int] * 7 + [ctypes.c_float, ctypes.c_int]
         )
         L.tyr_oracle_sdpa_online.restype = ctypes.c_int
+        L.tyr_oracle_sdpa_backward.argtypes = [f32p] * 7 + [ctypes.c_int] * 7 + [ctypes.c_float]
+        L.tyr_oracle_sdpa_backward.restype = ctypes.c_int
         L.tyr_oracle_merge2.argtypes = [f32p] * 6 + [ctypes.c_int64, ctypes.c_int]
         L.tyr_oracle_merge2.restype = None
         L.tyr_oracle_bf16_round.argtypes = [f32p, f32p, ctypes.c_int64]
@@ -58,6 +60,22 @@ def _c(a) -> np.ndarray:
 
 def threads() -> int:
     return int(lib().tyr_oracle_threads())
+
+
+def sdpa_backward(q, k, v, d_o, is_causal: bool, scale: float | None = None):
+    """Gradients of `sdpa` for the cotangent d_o: (d_q [B,Hq,Sq,D], d_k, d_v [B,Hkv,Skv,D])."""
+    q, k, v, d_o = _c(q), _c(k), _c(v), _c(d_o)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    assert k.shape == v.shape and k.shape[0] == B and k.shape[3] == D and d_o.shape == q.shape
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(D))
+    d_q, d_k, d_v = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    rc = lib().tyr_oracle_sdpa_backward(_p(q), _p(k), _p(v), _p(d_o), _p(d_q), _p(d_k), _p(d_v), B, Hq, Hkv,
+                                        Sq, Skv, D, int(bool(is_causal)), scale)
+    if rc != 0:
+        raise ValueError("tyr_oracle_sdpa_backward rejected its arguments")
+    return d_q, d_k, d_v
 
 
 def sdpa(q, k, v, is_causal: bool, scale: float | None = None, online_block: int = 0, window: int = 0,

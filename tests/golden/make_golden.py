@@ -1,6 +1,7 @@
 """Generate tests/golden/aten_sdpa.npz: outputs of the ATen operator the reference calls.
 
-Run from the repo root:  python tests/golden/make_golden.py
+Run from the repo root:  python tests/golden/make_golden.py [sdpa] [prologue] [keymask] [backward]
+(no argument: all of them).
 Every case calls `oracle.aten_path` (a restatement of the `lean_torch_sdpa_*`
 forwards of cc/src/tyr.cpp around torch's scaled_dot_product_attention) on fp32
 tensors whose values are bf16-representable, the reference's own fixture
@@ -103,7 +104,37 @@ def main_prologue():
     print(path, os.path.getsize(path), "bytes")
 
 
+# name: (B, Hq, Hkv, Sq, Skv, D, causal)
+BACKWARD_CASES = {
+    "mha_causal": (1, 2, 2, 40, 40, 64, True),
+    "gqa_causal": (1, 2, 1, 130, 130, 64, True),
+    "gqa_full_ragged": (1, 2, 1, 30, 140, 128, False),
+    "qkv_causal_topleft": (1, 2, 1, 135, 50, 64, True),
+}
+
+
+def main_backward():
+    """tests/golden/aten_backward.npz: gradients from torch autograd through the restated
+    lean_torch_sdpa_gqa (the derivative the reference's autograd.backward supplies)."""
+    out = {"torch_version": np.array(torch.__version__)}
+    for i, (name, (B, Hq, Hkv, Sq, Skv, D, causal)) in enumerate(BACKWARD_CASES.items()):
+        g = torch.Generator(device="cpu").manual_seed(4000 + i)
+        q = torch.randn(B, Hq, Sq, D, generator=g).bfloat16().float()
+        k = torch.randn(B, Hkv, Skv, D, generator=g).bfloat16().float()
+        v = torch.randn(B, Hkv, Skv, D, generator=g).bfloat16().float()
+        d_o = torch.randn(B, Hq, Sq, D, generator=g).bfloat16().float()
+        d_q, d_k, d_v = aten_path.sdpa_gqa_backward(q, k, v, d_o, causal)
+        for key, t in (("q", q), ("k", k), ("v", v), ("d_o", d_o)):
+            out[f"{name}.{key}"] = (t.numpy().view(np.uint32) >> 16).astype(np.uint16)
+        for key, t in (("d_q", d_q), ("d_k", d_k), ("d_v", d_v)):
+            out[f"{name}.{key}"] = t.numpy()
+        out[f"{name}.meta"] = np.array([B, Hq, Hkv, Sq, Skv, D, int(causal)])
+    path = os.path.join(os.path.dirname(__file__), "aten_backward.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    main()
-    main_prologue()
-    main_keymask()
+    jobs = {"sdpa": main, "prologue": main_prologue, "keymask": main_keymask, "backward": main_backward}
+    for name in (sys.argv[1:] or list(jobs)):
+        jobs[name]()

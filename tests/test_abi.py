@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(built_lib):
 
 
 def test_abi_version_and_error_strings(built_lib):
-    assert built_lib.tyr_b200_attn_abi_version() == 3
+    assert built_lib.tyr_b200_attn_abi_version() == 4
     assert built_lib.tyr_b200_attn_strerror(0) == b"ok"
     for code in range(1, 11):
         assert built_lib.tyr_b200_attn_strerror(-code).startswith(b"tyr_b200_attn:")
@@ -36,6 +36,8 @@ def test_struct_sizes_match_the_c_layout():
     # 5 pointers, 6 int32, 12 int64, int32 int32 float int32 int32 (+4 padding), pointer, int64
     assert ctypes.sizeof(_lib.PrefillArgs) == 5 * 8 + 6 * 4 + 12 * 8 + 5 * 4 + 4 + 8 + 8
     assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
+    # 10 pointers, uint64, 6 int32, 24 int64, int32 int32 float (+4 padding)
+    assert ctypes.sizeof(_lib.BackwardArgs) == 10 * 8 + 8 + 6 * 4 + 24 * 8 + 3 * 4 + 4
 
 
 def test_arguments_are_rejected_before_any_launch(built_lib):
@@ -62,6 +64,32 @@ def test_arguments_are_rejected_before_any_launch(built_lib):
     d = _lib.DecodeArgs()
     assert built_lib.tyr_b200_attn_decode(ctypes.byref(d), None) == -1
     assert built_lib.tyr_b200_attn_merge(None, None, None, None, None, None, 1, 64, None) == -1
+
+
+def test_backward_arguments_and_workspace(built_lib):
+    f = built_lib.tyr_b200_attn_backward_workspace_bytes
+    assert f(8, 16, 2048) == 2 * 8 * 16 * 2048 * 4
+    assert f(1, 2, 100) == 2 * 1 * 2 * 128 * 4              # rows padded to whole 128-row tiles
+    assert f(0, 2, 100) == 0
+    a = _lib.BackwardArgs()
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -1          # NULL pointers
+    buf = ctypes.create_string_buffer(8192)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    a.q = a.k = a.v = a.o = a.d_o = a.lse = a.d_q = a.d_k = a.d_v = p
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = 1, 3, 2, 4, 4, 64
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -2          # 3 % 2 != 0
+    a.n_head = 4
+    a.head_dim = 96
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -3          # head_dim
+    a.head_dim = 64
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride", "do_stride", "dq_stride", "dk_stride", "dv_stride"):
+        getattr(a, name)[:] = [4 * 4 * 64, 4 * 64, 64]
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -7          # no workspace
+    a.workspace, a.workspace_bytes = p, 16
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -7          # workspace too small
+    a.dtype = _lib.TYR_ATTN_F32
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(a), None) == -5          # bf16 only
 
 
 def test_decode_workspace_formula(built_lib):

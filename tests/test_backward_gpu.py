@@ -1,0 +1,118 @@
+"""Parity of the backward kernels (through the C ABI) with the oracle and the stored autograd gradients."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GRAD_REL_TO_MAX
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _bf16(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).bfloat16().to(_dev())
+
+
+def _run(q, k, v, d_o, causal, scale=None):
+    from tyr_b200 import nn as tnn
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=causal, scale=scale)
+    d_q, d_k, d_v = tnn.attentionBwd(q, k, v, o, lse, d_o, is_causal=causal, scale=scale)
+    torch.cuda.synchronize()
+    assert tnn.device_status(0, True) == 0
+    return d_q, d_k, d_v
+
+
+def _close(got, want, what):
+    got = got.float().cpu().numpy()
+    err = np.abs(got - want).max() / max(np.abs(want).max(), 1e-6)
+    assert np.isfinite(got).all(), what
+    assert err <= GRAD_REL_TO_MAX, f"{what}: max-abs error {err:.3e} of the largest entry"
+
+
+def test_golden_autograd_gradients(golden_backward):
+    for name, c in golden_backward.items():
+        causal = bool(c["meta"][6])
+        got = _run(_bf16(c["q"]), _bf16(c["k"]), _bf16(c["v"]), _bf16(c["d_o"]), causal)
+        for g, key in zip(got, ("d_q", "d_k", "d_v")):
+            _close(g, c[key], f"{name}.{key}")
+
+
+CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, causal
+    (1, 1, 1, 128, 128, 128, False),
+    (1, 1, 1, 128, 128, 128, True),
+    (2, 4, 2, 384, 384, 64, True),
+    (1, 2, 2, 200, 333, 128, False),
+    (2, 4, 1, 100, 100, 64, True),
+    (1, 2, 1, 128, 512, 128, True),      # more keys than queries: the late keys get zero gradient
+    (1, 2, 2, 512, 128, 128, True),      # more queries than keys
+    (1, 6, 2, 257, 257, 128, True),      # group of three, one row past a tile edge
+    (1, 8, 8, 1, 300, 64, False),        # a single query row
+    (3, 2, 1, 64, 64, 64, True),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,D,causal", CASES)
+def test_against_the_oracle(B, Hq, Hkv, Sq, Skv, D, causal):
+    g = torch.Generator().manual_seed(B * 1000 + Sq + Skv + D)
+    q, k, v, d_o = (torch.randn(s, generator=g).bfloat16() for s in
+                    ((B, Hq, Sq, D), (B, Hkv, Skv, D), (B, Hkv, Skv, D), (B, Hq, Sq, D)))
+    want = c_oracle.sdpa_backward(q.float().numpy(), k.float().numpy(), v.float().numpy(), d_o.float().numpy(), causal)
+    got = _run(q.to(_dev()), k.to(_dev()), v.to(_dev()), d_o.to(_dev()), causal)
+    for gt, w, key in zip(got, want, ("d_q", "d_k", "d_v")):
+        _close(gt, w, key)
+
+
+def test_custom_scale_and_strided_inputs():
+    """Q/K/V/dO as [B,S,H,D] views (the layout before transpose_for_attention) and a scale that is not 1/sqrt(D)."""
+    g = torch.Generator().manual_seed(11)
+    B, Hq, Hkv, S, D = 2, 4, 2, 160, 64
+    qs, ds = (torch.randn(B, S, Hq, D, generator=g).bfloat16() for _ in range(2))
+    ks, vs = (torch.randn(B, S, Hkv, D, generator=g).bfloat16() for _ in range(2))
+    q, k, v, d_o = (t.to(_dev()).transpose(1, 2) for t in (qs, ks, vs, ds))
+    scale = 0.2
+    want = c_oracle.sdpa_backward(*(t.float().cpu().contiguous().numpy() for t in (q, k, v, d_o)), True, scale)
+    from tyr_b200 import nn as tnn
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=True, scale=scale)
+    got = tnn.attentionBwd(q, k, v, o, lse, d_o, is_causal=True, scale=scale)
+    torch.cuda.synchronize()
+    for gt, w, key in zip(got, want, ("d_q", "d_k", "d_v")):
+        _close(gt, w, key)
+
+
+def test_linearity_in_the_cotangent():
+    """Gradients are linear in dO: bwd(2 dO) = 2 bwd(dO) bit for bit (a power of two scales every product exactly)."""
+    g = torch.Generator().manual_seed(12)
+    q, k, v, d_o = (torch.randn(1, 2, 256, 128, generator=g).bfloat16().to(_dev()) for _ in range(4))
+    a = _run(q, k, v, d_o, True)
+    b = _run(q, k, v, d_o * 2, True)
+    for x, y in zip(a, b):
+        assert torch.equal((x.float() * 2).bfloat16(), y)
+
+
+def test_keys_beyond_every_query_get_zero_gradient():
+    g = torch.Generator().manual_seed(13)
+    q, d_o = (torch.randn(1, 2, 100, 64, generator=g).bfloat16().to(_dev()) for _ in range(2))
+    k, v = (torch.randn(1, 1, 400, 64, generator=g).bfloat16().to(_dev()) for _ in range(2))
+    _, d_k, d_v = _run(q, k, v, d_o, True)
+    assert torch.count_nonzero(d_k[:, :, 100:]) == 0 and torch.count_nonzero(d_v[:, :, 100:]) == 0
+
+
+def test_workspace_is_checked_and_reusable():
+    from tyr_b200 import nn as tnn, _lib
+    g = torch.Generator().manual_seed(14)
+    q, k, v, d_o = (torch.randn(1, 2, 130, 64, generator=g).bfloat16().to(_dev()) for _ in range(4))
+    o, lse = tnn.attentionFwd(q, k, v)
+    need = _lib.load().tyr_b200_attn_backward_workspace_bytes(1, 2, 130)
+    assert need == 2 * 2 * 256 * 4
+    with pytest.raises(ValueError):
+        tnn.attentionBwd(q, k, v, o, lse, d_o, workspace=torch.empty(8, device=_dev()))
+    ws = torch.empty(need // 4, device=_dev())
+    a = tnn.attentionBwd(q, k, v, o, lse, d_o, workspace=ws)
+    b = tnn.attentionBwd(q, k, v, o, lse, d_o, workspace=ws)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)

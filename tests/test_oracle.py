@@ -196,3 +196,53 @@ def test_keymask_closed_forms():
     m0 = np.array([[0, 1, 1, 1, 1, 1]], np.uint8)                # causal row 0 sees only a padding key
     o, _ = c_oracle.sdpa(q, k, v, True, key_mask=m0)
     assert np.isnan(o[0, 0, 0]).all() and not np.isnan(o[0, 0, 1:]).any()
+
+
+def test_backward_oracle_matches_golden_autograd(golden_backward):
+    """The C restatement of the backward reproduces the stored torch-autograd gradients."""
+    for name, c in golden_backward.items():
+        B, Hq, Hkv, Sq, Skv, D, causal = (int(x) for x in c["meta"])
+        d_q, d_k, d_v = c_oracle.sdpa_backward(c["q"], c["k"], c["v"], c["d_o"], bool(causal))
+        for got, key in ((d_q, "d_q"), (d_k, "d_k"), (d_v, "d_v")):
+            np.testing.assert_allclose(got, c[key], rtol=0, atol=2e-5, err_msg=f"{name}.{key}")
+
+
+def test_backward_golden_still_matches_this_torch(golden_backward):
+    c = golden_backward["gqa_causal"]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    d_q, d_k, d_v = aten_path.sdpa_gqa_backward(t(c["q"]), t(c["k"]), t(c["v"]), t(c["d_o"]), True)
+    for got, key in ((d_q, "d_q"), (d_k, "d_k"), (d_v, "d_v")):
+        np.testing.assert_allclose(got.numpy(), c[key], rtol=0, atol=2e-5)
+
+
+def test_backward_oracle_against_finite_differences():
+    """d/dx of sum(O * dO) by central differences on a tiny case (fp64 would be exact to 1e-9;
+    the fp32 interface limits this check to a few 1e-3)."""
+    rng = np.random.default_rng(5)
+    B, Hq, Hkv, Sq, Skv, D = 1, 2, 1, 5, 7, 4
+    q, k, v, d_o = (rng.standard_normal(s).astype(np.float32) for s in
+                    ((B, Hq, Sq, D), (B, Hkv, Skv, D), (B, Hkv, Skv, D), (B, Hq, Sq, D)))
+    d_q, d_k, d_v = c_oracle.sdpa_backward(q, k, v, d_o, True)
+    loss = lambda q_, k_, v_: float((c_oracle.sdpa(q_, k_, v_, True)[0].astype(np.float64) * d_o).sum())
+    eps = 1e-2
+    for arr, grad, which in ((q, d_q, 0), (k, d_k, 1), (v, d_v, 2)):
+        for idx in [(0, 0, 1, 2), (0, arr.shape[1] - 1, 3, 0)]:
+            plus, minus = arr.copy(), arr.copy()
+            plus[idx] += eps
+            minus[idx] -= eps
+            args_p = [q, k, v]
+            args_m = [q, k, v]
+            args_p[which], args_m[which] = plus, minus
+            fd = (loss(*args_p) - loss(*args_m)) / (2 * eps)
+            assert abs(fd - grad[idx]) < 5e-3, (which, idx, fd, grad[idx])
+
+
+def test_backward_of_a_single_key_is_closed_form():
+    """One key: P = 1, so dV = sum of dO rows, dQ = 0, dK = 0."""
+    rng = np.random.default_rng(6)
+    q, d_o = rng.standard_normal((1, 2, 3, 8)).astype(np.float32), rng.standard_normal((1, 2, 3, 8)).astype(np.float32)
+    k, v = rng.standard_normal((1, 1, 1, 8)).astype(np.float32), rng.standard_normal((1, 1, 1, 8)).astype(np.float32)
+    d_q, d_k, d_v = c_oracle.sdpa_backward(q, k, v, d_o, False)
+    np.testing.assert_allclose(d_q, 0, atol=1e-6)
+    np.testing.assert_allclose(d_k, 0, atol=1e-6)
+    np.testing.assert_allclose(d_v[0, 0, 0], d_o.sum(axis=(0, 1, 2)), rtol=1e-5, atol=1e-6)
