@@ -25,7 +25,8 @@
 // or two accumulating products whose B operand is a streamed tile read MN-major.
 // Tensor memory (512 columns): S [0,128) dP [128,256) acc1 [256,256+D) acc2 [256+D,256+2D);
 // bf16 P / dS overwrite the first 64 columns of S / dP once those are in registers.
-// Warps: 0 TMA producer, 1 MMA issuer, 2 TMEM allocation, 4-7 elementwise + epilogue.
+// Warps: 0 TMA producer, 1 MMA issuer, 2 TMEM allocation, 4-11 elementwise + epilogue: two warps
+// per TMEM lane quarter, each on one half of the score columns (and of the output columns).
 // Every wait is bounded and reports through the per-device status word, as in the forward.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -39,7 +40,7 @@ namespace tyr {
 namespace {
 
 constexpr int kT = 128;           // tile rows and score-tile columns
-constexpr int kBwdThreads = 256;  // 8 warps
+constexpr int kBwdThreads = 384;  // 12 warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -50,7 +51,10 @@ struct BCfg {
   static constexpr int kStages = 2;
   static constexpr uint32_t kRes1 = 0, kRes2 = kTileBytes;
   static constexpr uint32_t kStr = 2 * kTileBytes;     // stage s: tile 1 at kStr + 2 s T, tile 2 one T further
-  static constexpr uint32_t kBarOff = kStr + kStages * 2 * kTileBytes;
+  // per stage: the streamed query block's 128 row statistics, two fp32 vectors (mode 0 only)
+  static constexpr uint32_t kStatOff = kStr + kStages * 2 * kTileBytes;
+  static constexpr uint32_t kStatBytes = 2 * kT * 4;
+  static constexpr uint32_t kBarOff = kStatOff + kStages * kStatBytes;
   // barriers
   static constexpr int res_full = 0;                   // resident pair landed
   static constexpr int str_full = 1;                   // [2] streamed pair landed
@@ -58,7 +62,9 @@ struct BCfg {
   static constexpr int s_full = 5;                     // S and dP in tensor memory
   static constexpr int p_full = 6;                     // P / dS written (one arrival per elementwise warp)
   static constexpr int acc_full = 7;                   // last accumulating product done
-  static constexpr int kNumBars = 8;
+  static constexpr int pair = 8;                       // [4] per lane quarter: the warp of the first column half
+                                                       //     has read the columns the other warp's P / dS overwrite
+  static constexpr int kNumBars = 12;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc1 = 256, kTmemAcc2 = 256 + D;
@@ -160,7 +166,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), i == C::p_full ? 4u : 1u);
+    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), i == C::p_full ? 8u : 1u);
     mbar_fence_init();
     tma_prefetch_desc(&tm_res1);
     tma_prefetch_desc(&tm_res2);
@@ -192,7 +198,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
         if (i >= C::kStages) ok = mbar_wait(bar(C::str_empty + s), ((i / C::kStages) - 1) & 1, abortp);
         if (!ok) break;
         const uint32_t dst = base + C::kStr + s * 2 * C::kTileBytes;
-        mbar_expect_tx(bar(C::str_full + s), 2 * C::kTileBytes);
+        mbar_expect_tx(bar(C::str_full + s), 2 * C::kTileBytes + (kMode == 0 ? C::kStatBytes : 0u));
+        if (kMode == 0) {
+          const int64_t at = ((int64_t)b * p.n_head + str_head(i)) * p.sq_pad + str_blk(i) * kT;
+          const uint32_t sdst = base + C::kStatOff + s * C::kStatBytes;
+          bulk_load(sdst, p.neg_lse2 + at, kT * 4, bar(C::str_full + s));
+          bulk_load(sdst + kT * 4, p.neg_delta_s + at, kT * 4, bar(C::str_full + s));
+        }
 #pragma unroll
         for (int kb = 0; kb < C::kBoxes; ++kb) {
           tma_load_4d(dst + kb * C::kBoxBytes, &tm_str1, bar(C::str_full + s), kb * 64, str_blk(i) * kT,
@@ -237,6 +249,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
   } else if (warp >= 4) {
     // ------------------------------------------------ elementwise + epilogue
     const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;   // score columns [64 half, 64 half + 64)
     const int r = quarter * 32 + lane;  // row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
@@ -251,6 +264,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
     }
     for (int i = 0; i < n_iter; ++i) {
       ok = mbar_wait(bar(C::s_full), i & 1, abortp);
+      // mode 0 reads the column statistics that landed with the streamed tiles: observe that
+      // barrier directly (it completed before the products were issued)
+      if (kMode == 0 && ok) ok = mbar_wait(bar(C::str_full + i % C::kStages), (i / C::kStages) & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -263,21 +279,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
         else c_limit = row0 + r - col0 + 1;
       }
       const bool masked = __any_sync(0xffffffffu, c_first > 0 || c_limit < kT);
-      const float* nl_col = nullptr;
-      const float* nd_col = nullptr;
-      if (kMode == 0) {
-        const int64_t at = ((int64_t)b * p.n_head + str_head(i)) * p.sq_pad + col0;
-        nl_col = p.neg_lse2 + at;
-        nd_col = p.neg_delta_s + at;
+      // mode 0: statistics of the 128 query columns, landed in shared memory with the tiles (the
+      // issuer waited for that stage before the products this warp was woken by)
+      const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
+                                                           (i % C::kStages) * C::kStatBytes);
+      const float* nd_col = nl_col + kT;
+      // This warp's two 32-column chunks of S and dP go to registers first.  bf16 P / dS of chunk
+      // c land on columns [16 c, 16 c + 16) of S / dP: the first half's results fall on its own
+      // chunk 0, the second half's on chunk 1 of the first half, which says on the pair barrier
+      // that it has read it; the second half passes that barrier before its first store.
+      uint32_t sr2[2][32], dp2[2][32];
+#pragma unroll
+      for (int step = 0; step < 2; ++step) {
+        tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
+        tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
+      }
+      tmem_wait_ld();
+#pragma unroll
+      for (int step = 0; step < 2; ++step) {
+        tmem_ld_ready(sr2[step]);
+        tmem_ld_ready(dp2[step]);
+      }
+      if (half == 0) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::pair + quarter));
       }
 #pragma unroll
-      for (int c = 0; c < kT / 32; ++c) {
-        uint32_t sr[32], dp[32];
-        tmem_ld32(tS + c * 32, sr);
-        tmem_ld32(tDP + c * 32, dp);
-        tmem_wait_ld();
-        tmem_ld_ready(sr);
-        tmem_ld_ready(dp);
+      for (int step = 0; step < 2; ++step) {
+        const int c = 2 * half + step;
+        uint32_t(&sr)[32] = sr2[step];
+        uint32_t(&dp)[32] = dp2[step];
         if (masked) {
 #pragma unroll
           for (int x = 0; x < 32; ++x)
@@ -307,9 +339,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
           pk_p[x] = pack_bf16x2(p0, p1);
           pk_s[x] = pack_bf16x2(d0, d1);
         }
+        if (step == 0 && half == 1) {
+          ok = mbar_wait(bar(C::pair + quarter), i & 1, abortp);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         if (kMode == 0) tmem_st16(tS + c * 16, pk_p);
         tmem_st16(tDP + c * 16, pk_s);
       }
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -331,7 +370,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
         const int64_t* st = which ? p.out2_stride : p.out1_stride;
         __nv_bfloat16* orow = (which ? p.out2 : p.out1) + b * st[0] + head * st[1] + (int64_t)row * st[2];
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t o[32];
           if (n_iter > 0) {
             tmem_ld32(tA + c * 32, o);
