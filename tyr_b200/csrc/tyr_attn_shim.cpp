@@ -182,4 +182,57 @@ extern "C" lean_object* lean_launch_tyrB200AttnDecode(b_lean_obj_arg q_, b_lean_
     return io_error(e.what());
   }
 }
+
+// Backward of the prefill call: dQ, dK, dV written in place into caller-allocated tensors.
+// Takes the place of LibTorch autograd's derivative of SDPA (`autograd.backward`,
+// Tyr/Torch.lean:742 -> cc/src/tyr.cpp:2111-2122) for callers that keep O and the LSE of
+// lean_launch_tyrB200AttnFwd.  `workspace` is a float32 CUDA tensor of at least
+// tyr_b200_attn_backward_workspace_bytes(batch, n_head, seq) bytes.
+extern "C" lean_object* lean_launch_tyrB200AttnBwd(b_lean_obj_arg q_, b_lean_obj_arg k_,
+                                                   b_lean_obj_arg v_, b_lean_obj_arg o_,
+                                                   b_lean_obj_arg lse_, b_lean_obj_arg d_o_,
+                                                   b_lean_obj_arg d_q_, b_lean_obj_arg d_k_,
+                                                   b_lean_obj_arg d_v_, b_lean_obj_arg workspace_,
+                                                   uint8_t is_causal, uint64_t stream,
+                                                   lean_object* /*w*/) {
+  try {
+    auto q = borrowTensor(q_), k = borrowTensor(k_), v = borrowTensor(v_), o = borrowTensor(o_),
+         lse = borrowTensor(lse_), d_o = borrowTensor(d_o_), d_q = borrowTensor(d_q_),
+         d_k = borrowTensor(d_k_), d_v = borrowTensor(d_v_), ws = borrowTensor(workspace_);
+    for (const auto* t : {&q, &k, &v, &o, &d_o, &d_q, &d_k, &d_v}) {
+      if (!t->is_cuda()) return io_error("tyrB200AttnBwd: tensors must be CUDA tensors");
+      if (t->dim() != 4) return io_error("tyrB200AttnBwd: tensors must be [batch, heads, seq, head_dim]");
+      if (t->scalar_type() != at::kBFloat16) return io_error("tyrB200AttnBwd: tensors must be bfloat16");
+      if (t->stride(3) != 1) return io_error("tyrB200AttnBwd: head_dim must have unit stride");
+    }
+    if (o.sizes() != q.sizes() || d_o.sizes() != q.sizes() || d_q.sizes() != q.sizes() ||
+        v.sizes() != k.sizes() || d_k.sizes() != k.sizes() || d_v.sizes() != k.sizes())
+      return io_error("tyrB200AttnBwd: shape mismatch");
+    if (!lse.is_cuda() || !lse.is_contiguous() || lse.scalar_type() != at::kFloat ||
+        lse.numel() != q.size(0) * q.size(1) * q.size(2))
+      return io_error("tyrB200AttnBwd: lse must be a contiguous float32 [batch, n_head, seq] CUDA tensor");
+    if (!ws.is_cuda() || !ws.is_contiguous())
+      return io_error("tyrB200AttnBwd: workspace must be a contiguous CUDA tensor");
+    TyrAttnBackwardArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
+    a.d_o = d_o.data_ptr(); a.lse = lse.data_ptr<float>();
+    a.d_q = d_q.data_ptr(); a.d_k = d_k.data_ptr(); a.d_v = d_v.data_ptr();
+    a.workspace = ws.data_ptr();
+    a.workspace_bytes = (uint64_t)ws.nbytes();
+    a.batch = (int32_t)q.size(0); a.n_head = (int32_t)q.size(1); a.n_kv_head = (int32_t)k.size(1);
+    a.q_seq = (int32_t)q.size(2); a.kv_seq = (int32_t)k.size(2); a.head_dim = (int32_t)q.size(3);
+    fill_strides(a.q_stride, q); fill_strides(a.k_stride, k); fill_strides(a.v_stride, v);
+    fill_strides(a.o_stride, o); fill_strides(a.do_stride, d_o); fill_strides(a.dq_stride, d_q);
+    fill_strides(a.dk_stride, d_k); fill_strides(a.dv_stride, d_v);
+    a.dtype = TYR_ATTN_BF16;
+    a.is_causal = is_causal != 0;
+    a.scale = 0.f;
+    int rc = tyr_b200_attn_backward(&a, reinterpret_cast<void*>(stream));
+    if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
+    return lean_io_result_mk_ok(lean_box(0));
+  } catch (const std::exception& e) {
+    return io_error(e.what());
+  }
+}
 #endif  // TYR_B200_SHIM_ENABLED

@@ -25,6 +25,14 @@ opaque tyrB200AttnFwd.launch
 opaque tyrB200AttnDecode.launch
     (q kCache vCache out workspace : @& Tensor) (kvLen : UInt64) (stream : Tyr.GPU.CudaStream) : IO Unit
 
+/-- Backward of `tyrB200AttnFwd`: `dQ dK dV` written in place from `dO`, the forward's inputs, its
+    output and its LSE.  `workspace`: float32, `2 * b * hq * ceil(s/128)*128` elements.
+    C side: `lean_launch_tyrB200AttnBwd`. -/
+@[extern "lean_launch_tyrB200AttnBwd"]
+opaque tyrB200AttnBwd.launch
+    (q k v out lse dOut dQ dK dV workspace : @& Tensor) (isCausal : UInt8)
+    (stream : Tyr.GPU.CudaStream) : IO Unit
+
 /-- Typed wrapper: output and per-row LSE of causal / non-causal GQA attention. -/
 def attentionFwd {b hq hkv s d : UInt64}
     (q : T #[b, hq, s, d]) (k v : T #[b, hkv, s, d]) (isCausal : Bool := true)
@@ -35,5 +43,19 @@ def attentionFwd {b hq hkv s d : UInt64}
   let stream ← torch.cuda_current_stream
   tyrB200AttnFwd.launch q k v out lse32 (if isCausal then 1 else 0) stream
   pure (out, lse32)
+
+/-- Typed wrapper of the backward: gradients with the shapes of `q`, `k`, `v`. -/
+def attentionBwd {b hq hkv s d : UInt64}
+    (q : T #[b, hq, s, d]) (k v : T #[b, hkv, s, d]) (out : T #[b, hq, s, d]) (lse : T #[b, hq, s])
+    (dOut : T #[b, hq, s, d]) (isCausal : Bool := true)
+    : IO (T #[b, hq, s, d] × T #[b, hkv, s, d] × T #[b, hkv, s, d]) := do
+  let dQ : T #[b, hq, s, d] := torch.zeros_like q
+  let dK : T #[b, hkv, s, d] := torch.zeros_like k
+  let dV : T #[b, hkv, s, d] := torch.zeros_like v
+  let rows := ((s + 127) / 128) * 128
+  let ws : T #[2, b, hq, rows] := torch.toFloat' (torch.zeros #[2, b, hq, rows] false (torch.device q))
+  let stream ← torch.cuda_current_stream
+  tyrB200AttnBwd.launch q k v out lse dOut dQ dK dV ws (if isCausal then 1 else 0) stream
+  pure (dQ, dK, dV)
 
 end Tyr.GPU.B200
