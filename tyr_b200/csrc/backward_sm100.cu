@@ -416,6 +416,266 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// dQ kernel with the score products running ahead of the elementwise step.
+// One CTA per 128 query rows of a (batch, query head): Q and dO stay in shared memory, K streams
+// through a 3-stage ring and V through a 2-stage ring.  dS does not overlay dP here: tensor memory
+// has 128 columns to spare next to S, dP and dQ, enough for two bf16 dS buffers.  S and dP may
+// therefore be overwritten as soon as the elementwise warps hold them in registers, so
+// S(i+1) = Q K(i+1)^T and dP(i+1) = dO V(i+1)^T are computed while dS(i) is being formed, and
+// dQ += dS(i) K(i) follows; the elementwise warps go from one tile to the next without waiting.
+// (V is free once dP has read it, K only after the dQ product: hence the deeper K ring.)
+template <int D>
+struct DqCfg {
+  static constexpr int kBoxes = D / 64;
+  static constexpr uint32_t kBoxBytes = 128u * 128u;
+  static constexpr uint32_t kTileBytes = kBoxes * kBoxBytes;
+  static constexpr int kKStages = 3, kVStages = 2;
+  static constexpr uint32_t kQ = 0, kDO = kTileBytes, kK = 2 * kTileBytes;
+  static constexpr uint32_t kV = kK + kKStages * kTileBytes;
+  static constexpr uint32_t kBarOff = kV + kVStages * kTileBytes;
+  static constexpr int res_full = 0;
+  static constexpr int k_full = 1;                       // [3]
+  static constexpr int k_empty = k_full + kKStages;      // [3] the dQ product has read the K tile
+  static constexpr int v_full = k_empty + kKStages;      // [2]
+  static constexpr int v_empty = v_full + kVStages;      // [2] the dP product has read the V tile
+  static constexpr int s_full = v_empty + kVStages;      // S and dP in tensor memory
+  static constexpr int sdp_free = s_full + 1;            // S and dP are in registers (8 warp arrivals)
+  static constexpr int p_full = sdp_free + 1;            // [2] dS buffer written (8 warp arrivals), alternating
+  static constexpr int acc_full = p_full + 2;
+  static constexpr int kNumBars = acc_full + 1;
+  static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc = 256, kTmemDS = 384;  // dS: 2 x 64 columns
+  static_assert(256 + D + 128 <= 512, "tensor memory budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+              const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+              const BwdParams p) {
+  using C = DqCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t sBar = base + C::kBarOff;
+  auto bar = [&](int i) { return sBar + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // the query blocks with the most key blocks (the last ones under a causal mask) come first
+  const int lvl = blockIdx.x / (p.n_head * p.batch);
+  const int rem = blockIdx.x - lvl * p.n_head * p.batch;
+  const int head = rem % p.n_head, b = rem / p.n_head;
+  const int blk = p.n_qblk - 1 - lvl;
+  const int row0 = blk * kT;
+  const int hkv = head / p.group;
+  const int n_iter = p.causal ? min(p.n_kblk, blk + 1) : p.n_kblk;  // key blocks 0 .. n_iter-1
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < C::kNumBars; ++i)
+      mbar_init(bar(i), (i == C::sdp_free || i == C::p_full || i == C::p_full + 1) ? 8u : 1u);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
+#pragma unroll
+      for (int kb = 0; kb < C::kBoxes; ++kb) {
+        tma_load_4d(base + C::kQ + kb * C::kBoxBytes, &tm_q, bar(C::res_full), kb * 64, row0, head, b);
+        tma_load_4d(base + C::kDO + kb * C::kBoxBytes, &tm_do, bar(C::res_full), kb * 64, row0, head, b);
+      }
+      bool ok = true;
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int ks = i % C::kKStages, vs = i % C::kVStages;
+        if (i >= C::kKStages) ok = mbar_wait(bar(C::k_empty + ks), ((i / C::kKStages) - 1) & 1, abortp);
+        if (!ok) break;
+        mbar_expect_tx(bar(C::k_full + ks), C::kTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < C::kBoxes; ++kb)
+          tma_load_4d(base + C::kK + ks * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(C::k_full + ks), kb * 64,
+                      i * kT, hkv, b);
+        if (i >= C::kVStages) ok = mbar_wait(bar(C::v_empty + vs), ((i / C::kVStages) - 1) & 1, abortp);
+        if (!ok) break;
+        mbar_expect_tx(bar(C::v_full + vs), C::kTileBytes);
+#pragma unroll
+        for (int kb = 0; kb < C::kBoxes; ++kb)
+          tma_load_4d(base + C::kV + vs * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(C::v_full + vs), kb * 64,
+                      i * kT, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP, tAcc = tmem + C::kTmemAcc;
+      const uint32_t q_lo = umma_desc_lo(base + C::kQ, 16), do_lo = umma_desc_lo(base + C::kDO, 16);
+      auto scores = [&](int i) {  // S = Q K(i)^T, dP = dO V(i)^T; V(i) is free afterwards
+        const int ks = i % C::kKStages, vs = i % C::kVStages;
+        if (!mbar_wait(bar(C::k_full + ks), (i / C::kKStages) & 1, abortp)) return false;
+        if (!mbar_wait(bar(C::v_full + vs), (i / C::kVStages) & 1, abortp)) return false;
+        tc_fence_after();
+        issue_nt<D>(tS, q_lo, umma_desc_lo(base + C::kK + ks * C::kTileBytes, 16));
+        issue_nt<D>(tDP, do_lo, umma_desc_lo(base + C::kV + vs * C::kTileBytes, 16));
+        umma_commit(bar(C::s_full));
+        umma_commit(bar(C::v_empty + vs));
+        return true;
+      };
+      bool ok = mbar_wait(bar(C::res_full), 0, abortp);
+      if (ok) ok = scores(0);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        if (i + 1 < n_iter) {
+          // S(i) and dP(i) are in the elementwise warps' registers: the next pair may overwrite them
+          ok = mbar_wait(bar(C::sdp_free), i & 1, abortp);
+          if (ok) ok = scores(i + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(bar(C::p_full + (i & 1)), (i >> 1) & 1, abortp);
+        if (!ok) break;
+        tc_fence_after();
+        const int ks = i % C::kKStages;
+        issue_acc<D>(tAcc, tmem + C::kTmemDS + (i & 1) * 64,
+                     umma_desc_lo(base + C::kK + ks * C::kTileBytes, C::kBoxBytes), i > 0);
+        umma_commit(bar(C::k_empty + ks));
+      }
+      if (ok) umma_commit(bar(C::acc_full));
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------ elementwise + epilogue
+    const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;   // key columns [64 half, 64 half + 64)
+    const int r = quarter * 32 + lane;  // query row of the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
+    const uint64_t sl2x2 = pack_f32x2(p.sl2, p.sl2), scale2 = pack_f32x2(p.scale, p.scale);
+    const int64_t at = ((int64_t)b * p.n_head + head) * p.sq_pad + row0 + r;
+    const float nl_row = p.neg_lse2[at], nd_row = p.neg_delta_s[at];
+    const uint64_t nl2 = pack_f32x2(nl_row, nl_row), nd2 = pack_f32x2(nd_row, nd_row);
+    bool ok = true;
+    for (int i = 0; i < n_iter; ++i) {
+      ok = mbar_wait(bar(C::s_full), i & 1, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr2[2][32], dp2[2][32];
+#pragma unroll
+      for (int step = 0; step < 2; ++step) {
+        tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
+        tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
+      }
+      tmem_wait_ld();
+#pragma unroll
+      for (int step = 0; step < 2; ++step) {
+        tmem_ld_ready(sr2[step]);
+        tmem_ld_ready(dp2[step]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::sdp_free));
+
+      // keys this query row keeps under the causal mask: key <= query
+      const int c_limit = p.causal ? row0 + r - i * kT + 1 : kT;
+      const bool masked = __any_sync(0xffffffffu, c_limit < kT);
+      const uint32_t tDS = tmem + lane_addr + C::kTmemDS + (i & 1) * 64;
+#pragma unroll
+      for (int step = 0; step < 2; ++step) {
+        const int c = 2 * half + step;
+        uint32_t(&sr)[32] = sr2[step];
+        uint32_t(&dp)[32] = dp2[step];
+        if (masked) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
+        }
+        uint32_t pk_s[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, nl2);
+          float t0, t1;
+          unpack_f32x2(t2, t0, t1);
+          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+          const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, nd2);
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
+          pk_s[x] = pack_bf16x2(d0, d1);
+        }
+        tmem_st16(tDS + c * 16, pk_s);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::p_full + (i & 1)));
+    }
+
+    // epilogue: dQ -> bf16 -> global, one row per thread, half of the columns per warp of the pair
+    if (ok) {
+      ok = mbar_wait(bar(C::acc_full), 0, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int row = row0 + r;
+      const bool row_ok = row < p.q_seq;
+      const uint32_t tA = tmem + lane_addr + C::kTmemAcc;
+      __nv_bfloat16* orow = p.out1 + b * p.out1_stride[0] + head * p.out1_stride[1] + (int64_t)row * p.out1_stride[2];
+#pragma unroll
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t o[32];
+        tmem_ld32(tA + c * 32, o);
+        tmem_wait_ld();
+        tmem_ld_ready(o);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 wv;
+          wv.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]), __uint_as_float(o[q4 * 8 + 1]));
+          wv.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]));
+          wv.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]));
+          wv.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]));
+          if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = wv;
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  // ------------------------------------------------------------------ exit
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) {
+      }
+      atomicOr(p.status, abort_flag);
+    }
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
 // Row statistics of the backward: one group of D/8 lanes per query row, 16-byte loads.
 template <int D>
 __global__ void __launch_bounds__(256)
@@ -484,7 +744,17 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
   if ((rc = make_tile_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
   if ((rc = make_tile_map(&tdo, a.d_o, a.batch, a.n_head, a.q_seq, D, a.do_stride))) return rc;
   if ((rc = set_smem_attr<D, 0>())) return rc;
-  if ((rc = set_smem_attr<D, 1>())) return rc;
+  {
+    static std::atomic<bool> attr_set[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
+      cudaError_t e = cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)DqCfg<D>::kSmemBytes);
+      if (e != cudaSuccess) return (int)e;
+      attr_set[dev].store(true, std::memory_order_release);
+    }
+  }
 
   {
     constexpr int kLanes = D / 8;
@@ -538,7 +808,7 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
     p.out1_stride[i] = a.dq_stride[i];
     p.out2_stride[i] = 0;
   }
-  bwd_kernel<D, 1><<<(unsigned)grid_q, kBwdThreads, C::kSmemBytes, st>>>(tq, tdo, tk, tv, p);
+  bwd_dq_kernel<D><<<(unsigned)grid_q, kBwdThreads, DqCfg<D>::kSmemBytes, st>>>(tq, tdo, tk, tv, p);
   count_launch();
   return (int)cudaGetLastError();
 }
