@@ -10,27 +10,28 @@
 // Three launches:
 //   bwd_rowstats_kernel : -lse*log2(e) and -delta*scale per query row, padded to whole tiles
 //                         (padding rows get -inf / 0, so they produce P = 0 downstream).
-//   bwd_kernel<D, 0>    : one CTA per 128 keys of a (batch, KV head).  K and V tiles stay in
-//                         shared memory; the Q and dO tiles of every query head of the group and
-//                         every query block the keys are visible to stream through a 2-stage TMA
-//                         ring.  Transposed orientation (rows = keys): S^T = K Q^T, dP^T = V dO^T
-//                         by tcgen05.mma from shared memory into tensor memory, P^T and dS^T go
-//                         back to tensor memory as bf16 and feed dV += P^T dO, dK += dS^T Q as the
-//                         A operand.  dK and dV accumulate in tensor memory over the whole group:
-//                         no atomics, a deterministic sum.
-//   bwd_kernel<D, 1>    : one CTA per 128 query rows of a (batch, query head).  Q and dO stay,
-//                         K and V stream; S = Q K^T, dP = dO V^T, dS to tensor memory, dQ += dS K.
-// Both instantiations are the same program: a resident tile pair, a streamed tile pair, two
-// score-shaped products, an elementwise step by four warps (thread = row = TMEM lane), then one
-// or two accumulating products whose B operand is a streamed tile read MN-major.
-// Tensor memory (512 columns): S [0,128) dP [128,256) acc1 [256,256+D) acc2 [256+D,256+2D);
-// bf16 P / dS overwrite the first 64 columns of S / dP once those are in registers.
-// Warps: 0 TMA producer, 1 MMA issuer, 2 TMEM allocation, 4-11 elementwise + epilogue: two warps
-// per TMEM lane quarter, each on one half of the score columns (and of the output columns).
+//   bwd_dkdv_kernel<D>  : persistent; one work unit = 128 keys of a (batch, KV head).  K and V tiles
+//                         stay in shared memory; the Q and dO tiles of every query head of the group
+//                         and every query block the keys are visible to stream through a 2-stage TMA
+//                         ring, together with that block's row statistics.  Transposed orientation
+//                         (rows = keys): S^T = K Q^T, dP^T = V dO^T by tcgen05.mma from shared memory
+//                         into tensor memory, P^T and dS^T go back to tensor memory as bf16 and feed
+//                         dV += P^T dO, dK += dS^T Q as the A operand, the streamed tile read MN-major
+//                         as B.  dK and dV accumulate in tensor memory over the whole group: no
+//                         atomics, a deterministic sum.  Tensor memory (512 columns): S^T [0,128)
+//                         dP^T [128,256) dK [256,256+D) dV [256+D,256+2D); bf16 P^T / dS^T overwrite the
+//                         first 64 columns of S^T / dP^T once those are in registers.
+//   bwd_dq_kernel<D>    : persistent; one work unit = 128 query rows of a (batch, query head).  Q and
+//                         dO stay, K and V stream; S = Q K^T, dP = dO V^T, dQ += dS K, with dS in two
+//                         buffers of its own so that the next score products run while dS is formed.
+// Warps of both: 0 TMA producer, 1 MMA issuer, 2 TMEM allocation, 4-11 elementwise + epilogue, two
+// warps per TMEM lane quarter (thread = row), each on one half of the score columns and of the
+// output columns.  Units are sorted by decreasing work and dealt to the CTAs in mirrored rounds.
 // Every wait is bounded and reports through the per-device status word, as in the forward.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <atomic>
 
 #include "attn_internal.h"
@@ -64,7 +65,9 @@ struct BCfg {
   static constexpr int acc_full = 7;                   // last accumulating product done
   static constexpr int pair = 8;                       // [4] per lane quarter: the warp of the first column half
                                                        //     has read the columns the other warp's P / dS overwrite
-  static constexpr int kNumBars = 12;
+  static constexpr int res_empty = 12;                 // the unit's last score products have read K and V
+  static constexpr int acc_free = 13;                  // the epilogue has read dK and dV (8 warp arrivals)
+  static constexpr int kNumBars = 14;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc1 = 256, kTmemAcc2 = 256 + D;
@@ -119,13 +122,45 @@ __device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint
   }
 }
 
-// kMode 0: rows = keys, resident (K, V), streamed (Q, dO), out1 = dK, out2 = dV.
-// kMode 1: rows = queries, resident (Q, dO), streamed (K, V), out1 = dQ.
-template <int D, int kMode>
+// Static schedule of the persistent kernels: in round k CTA c takes unit k G + c, mirrored in odd
+// rounds (k G + G - 1 - c) so that the CTAs' totals even out over units sorted by decreasing work.
+__device__ __forceinline__ int unit_of_round(int round, int n_units) {
+  const int G = gridDim.x, c = blockIdx.x;
+  const int u = round * G + ((round & 1) ? G - 1 - c : c);
+  return u < n_units ? u : -1;
+}
+__device__ __forceinline__ int rounds_of(int n_units) { return (n_units + gridDim.x - 1) / gridDim.x; }
+
+// One work unit of the dK/dV kernel: 128 keys of a (batch, KV head).  Units are numbered with the
+// heaviest first (key block 0 is seen by every query block under a causal mask).
+struct KvUnit {
+  int blk, head, b;
+  int lo;        // first query block with a row >= the unit's first key
+  int per_head;  // query blocks streamed per query head
+  int n_iter;    // per_head * group; 0 when no query sees these keys
+};
+__device__ __forceinline__ KvUnit kv_unit(int u, const BwdParams& p) {
+  KvUnit w;
+  const int lvl = u / (p.n_kv_head * p.batch);
+  const int rem = u - lvl * p.n_kv_head * p.batch;
+  w.head = rem % p.n_kv_head;
+  w.b = rem / p.n_kv_head;
+  w.blk = lvl;
+  w.lo = p.causal ? min(w.blk, p.n_qblk) : 0;
+  w.per_head = p.n_qblk - w.lo;
+  w.n_iter = w.per_head * p.group;
+  return w;
+}
+
+// dK / dV kernel, persistent: CTA c works on units c, c + gridDim.x, ...  Rows = keys.  The K and V
+// tiles of the unit stay in shared memory (the next unit's are fetched as soon as the unit's last
+// score products have read them), Q and dO stream.  Barrier phases run on across units: every role
+// counts streamed tile pairs (`it`) and units with work (`rc`) for itself.
+template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ CUtensorMap tm_res2,
-           const __grid_constant__ CUtensorMap tm_str1, const __grid_constant__ CUtensorMap tm_str2,
-           const BwdParams p) {
+bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                const BwdParams p) {
   using C = BCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_slot;
@@ -136,42 +171,17 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
   const uint32_t sBar = base + C::kBarOff;
   auto bar = [&](int i) { return sBar + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // work unit of this CTA; the heaviest units (most streamed tiles under a causal mask) come first
-  int blk, head, b;
-  {
-    const int n_blk = kMode == 0 ? p.n_kblk : p.n_qblk;
-    const int heads = kMode == 0 ? p.n_kv_head : p.n_head;
-    const int lvl = blockIdx.x / (heads * p.batch);
-    const int rem = blockIdx.x - lvl * heads * p.batch;
-    head = rem % heads;
-    b = rem / heads;
-    blk = kMode == 0 ? lvl : n_blk - 1 - lvl;
-  }
-  const int row0 = blk * kT;  // first key (mode 0) / query (mode 1) of the resident tiles
-  // streamed tiles: mode 0: query blocks [lo, n_qblk) of each of `group` query heads;
-  //                 mode 1: key blocks [0, hi]
-  int lo = 0, per_head, n_iter;
-  if (kMode == 0) {
-    lo = p.causal ? min(blk, p.n_qblk) : 0;  // first query block with a row >= the first key
-    per_head = p.n_qblk - lo;
-    n_iter = per_head * p.group;
-  } else {
-    per_head = p.causal ? min(p.n_kblk, blk + 1) : p.n_kblk;
-    n_iter = per_head;
-  }
-  const int res_head = head;
-  auto str_head = [&](int i) { return kMode == 0 ? head * p.group + i / per_head : head / p.group; };
-  auto str_blk = [&](int i) { return kMode == 0 ? lo + i % per_head : i; };
+  const int n_units = p.n_kblk * p.n_kv_head * p.batch;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < C::kNumBars; ++i) mbar_init(bar(i), i == C::p_full ? 8u : 1u);
+    for (int i = 0; i < C::kNumBars; ++i)
+      mbar_init(bar(i), (i == C::p_full || i == C::acc_free) ? 8u : 1u);
     mbar_fence_init();
-    tma_prefetch_desc(&tm_res1);
-    tma_prefetch_desc(&tm_res2);
-    tma_prefetch_desc(&tm_str1);
-    tma_prefetch_desc(&tm_str2);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
@@ -185,200 +195,214 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0 && n_iter > 0) {
-      mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
-#pragma unroll
-      for (int kb = 0; kb < C::kBoxes; ++kb) {
-        tma_load_4d(base + C::kRes1 + kb * C::kBoxBytes, &tm_res1, bar(C::res_full), kb * 64, row0, res_head, b);
-        tma_load_4d(base + C::kRes2 + kb * C::kBoxBytes, &tm_res2, bar(C::res_full), kb * 64, row0, res_head, b);
-      }
+    if (lane == 0) {
       bool ok = true;
-      for (int i = 0; i < n_iter && ok; ++i) {
-        const int s = i % C::kStages;
-        if (i >= C::kStages) ok = mbar_wait(bar(C::str_empty + s), ((i / C::kStages) - 1) & 1, abortp);
+      int it = 0, rc = 0;
+      for (int round = 0; round < rounds_of(n_units) && ok; ++round) {
+        const int u = unit_of_round(round, n_units);
+        if (u < 0) continue;
+        const KvUnit w = kv_unit(u, p);
+        if (w.n_iter == 0) continue;
+        if (rc > 0) ok = mbar_wait(bar(C::res_empty), (rc - 1) & 1, abortp);
         if (!ok) break;
-        const uint32_t dst = base + C::kStr + s * 2 * C::kTileBytes;
-        mbar_expect_tx(bar(C::str_full + s), 2 * C::kTileBytes + (kMode == 0 ? C::kStatBytes : 0u));
-        if (kMode == 0) {
-          const int64_t at = ((int64_t)b * p.n_head + str_head(i)) * p.sq_pad + str_blk(i) * kT;
-          const uint32_t sdst = base + C::kStatOff + s * C::kStatBytes;
-          bulk_load(sdst, p.neg_lse2 + at, kT * 4, bar(C::str_full + s));
-          bulk_load(sdst + kT * 4, p.neg_delta_s + at, kT * 4, bar(C::str_full + s));
-        }
+        mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
 #pragma unroll
         for (int kb = 0; kb < C::kBoxes; ++kb) {
-          tma_load_4d(dst + kb * C::kBoxBytes, &tm_str1, bar(C::str_full + s), kb * 64, str_blk(i) * kT,
-                      str_head(i), b);
-          tma_load_4d(dst + C::kTileBytes + kb * C::kBoxBytes, &tm_str2, bar(C::str_full + s), kb * 64,
-                      str_blk(i) * kT, str_head(i), b);
+          tma_load_4d(base + C::kRes1 + kb * C::kBoxBytes, &tm_k, bar(C::res_full), kb * 64, w.blk * kT, w.head, w.b);
+          tma_load_4d(base + C::kRes2 + kb * C::kBoxBytes, &tm_v, bar(C::res_full), kb * 64, w.blk * kT, w.head, w.b);
         }
+        for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
+          const int s = it % C::kStages;
+          if (it >= C::kStages) ok = mbar_wait(bar(C::str_empty + s), ((it / C::kStages) - 1) & 1, abortp);
+          if (!ok) break;
+          const int hq = w.head * p.group + i / w.per_head, qblk = w.lo + i % w.per_head;
+          const uint32_t dst = base + C::kStr + s * 2 * C::kTileBytes;
+          mbar_expect_tx(bar(C::str_full + s), 2 * C::kTileBytes + C::kStatBytes);
+          {
+            const int64_t at = ((int64_t)w.b * p.n_head + hq) * p.sq_pad + qblk * kT;
+            const uint32_t sdst = base + C::kStatOff + s * C::kStatBytes;
+            bulk_load(sdst, p.neg_lse2 + at, kT * 4, bar(C::str_full + s));
+            bulk_load(sdst + kT * 4, p.neg_delta_s + at, kT * 4, bar(C::str_full + s));
+          }
+#pragma unroll
+          for (int kb = 0; kb < C::kBoxes; ++kb) {
+            tma_load_4d(dst + kb * C::kBoxBytes, &tm_q, bar(C::str_full + s), kb * 64, qblk * kT, hq, w.b);
+            tma_load_4d(dst + C::kTileBytes + kb * C::kBoxBytes, &tm_do, bar(C::str_full + s), kb * 64, qblk * kT,
+                        hq, w.b);
+          }
+        }
+        ++rc;
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_iter > 0) {
+    if (lane == 0) {
       const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP;
       const uint32_t tA1 = tmem + C::kTmemAcc1, tA2 = tmem + C::kTmemAcc2;
       const uint32_t res1_lo = umma_desc_lo(base + C::kRes1, 16), res2_lo = umma_desc_lo(base + C::kRes2, 16);
-      auto scores = [&](int i) {  // S = res1 str1^T, dP = res2 str2^T
-        const int s = i % C::kStages;
+      auto scores = [&](int g) {  // S^T = K Q^T, dP^T = V dO^T for streamed pair number g
+        const int s = g % C::kStages;
         const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
-        if (!mbar_wait(bar(C::str_full + s), (i / C::kStages) & 1, abortp)) return false;
+        if (!mbar_wait(bar(C::str_full + s), (g / C::kStages) & 1, abortp)) return false;
         tc_fence_after();
         issue_nt<D>(tS, res1_lo, umma_desc_lo(t1, 16));
         issue_nt<D>(tDP, res2_lo, umma_desc_lo(t1 + C::kTileBytes, 16));
         umma_commit(bar(C::s_full));
         return true;
       };
-      bool ok = mbar_wait(bar(C::res_full), 0, abortp);
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_iter && ok; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
-        ok = mbar_wait(bar(C::p_full), i & 1, abortp);
-        if (!ok) break;
-        tc_fence_after();
-        // dS (bf16, over the first columns of dP) times the first streamed tile, MN-major
-        issue_acc<D>(tA1, tDP, umma_desc_lo(t1, C::kBoxBytes), i > 0);
-        if (kMode == 0) issue_acc<D>(tA2, tS, umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes), i > 0);
-        umma_commit(bar(C::str_empty + s));
-        if (i + 1 < n_iter) ok = scores(i + 1);
-        else umma_commit(bar(C::acc_full));
+      bool ok = true;
+      int it = 0, rc = 0;
+      for (int round = 0; round < rounds_of(n_units) && ok; ++round) {
+        const int u = unit_of_round(round, n_units);
+        if (u < 0) continue;
+        const KvUnit w = kv_unit(u, p);
+        if (w.n_iter == 0) continue;
+        ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
+        if (ok) ok = scores(it);
+        if (ok && w.n_iter == 1) umma_commit(bar(C::res_empty));
+        for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
+          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
+          // the unit's first accumulating products overwrite dK / dV: the previous unit's
+          // epilogue must have read them
+          if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc<D>(tA1, tDP, umma_desc_lo(t1, C::kBoxBytes), i > 0);                    // dK += dS^T Q
+          issue_acc<D>(tA2, tS, umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes), i > 0);     // dV += P^T dO
+          umma_commit(bar(C::str_empty + s));
+          if (i + 1 < w.n_iter) {
+            ok = scores(it + 1);
+            // K and V are read by the score products only: after the unit's last pair of them
+            // the producer may fetch the next unit's
+            if (ok && i + 2 == w.n_iter) umma_commit(bar(C::res_empty));
+          } else {
+            umma_commit(bar(C::acc_full));
+          }
+        }
+        ++rc;
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------ elementwise + epilogue
     const int quarter = warp & 3;
-    const int half = (warp - 4) >> 2;   // score columns [64 half, 64 half + 64)
-    const int r = quarter * 32 + lane;  // row of the tile = TMEM lane
+    const int half = (warp - 4) >> 2;   // query columns [64 half, 64 half + 64), output columns likewise
+    const int r = quarter * 32 + lane;  // key row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
     const uint64_t sl2x2 = pack_f32x2(p.sl2, p.sl2), scale2 = pack_f32x2(p.scale, p.scale);
     bool ok = true;
-    // mode 1: this thread's row statistics
-    float nl_row = 0.f, nd_row = 0.f;
-    if (kMode == 1) {
-      const int64_t at = ((int64_t)b * p.n_head + head) * p.sq_pad + row0 + r;
-      nl_row = p.neg_lse2[at];
-      nd_row = p.neg_delta_s[at];
-    }
-    for (int i = 0; i < n_iter; ++i) {
-      ok = mbar_wait(bar(C::s_full), i & 1, abortp);
-      // mode 0 reads the column statistics that landed with the streamed tiles: observe that
-      // barrier directly (it completed before the products were issued)
-      if (kMode == 0 && ok) ok = mbar_wait(bar(C::str_full + i % C::kStages), (i / C::kStages) & 1, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int col0 = str_blk(i) * kT;  // first query (mode 0) / key (mode 1) of the score columns
-      // columns this row keeps under the causal mask: mode 0 (row = key): query >= key;
-      // mode 1 (row = query): key <= query
-      int c_first = 0, c_limit = kT;
-      if (p.causal) {
-        if (kMode == 0) c_first = row0 + r - col0;
-        else c_limit = row0 + r - col0 + 1;
-      }
-      const bool masked = __any_sync(0xffffffffu, c_first > 0 || c_limit < kT);
-      // mode 0: statistics of the 128 query columns, landed in shared memory with the tiles (the
-      // issuer waited for that stage before the products this warp was woken by)
-      const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
-                                                           (i % C::kStages) * C::kStatBytes);
-      const float* nd_col = nl_col + kT;
-      // This warp's two 32-column chunks of S and dP go to registers first.  bf16 P / dS of chunk
-      // c land on columns [16 c, 16 c + 16) of S / dP: the first half's results fall on its own
-      // chunk 0, the second half's on chunk 1 of the first half, which says on the pair barrier
-      // that it has read it; the second half passes that barrier before its first store.
-      uint32_t sr2[2][32], dp2[2][32];
+    int it = 0, rc = 0;
+    for (int round = 0; round < rounds_of(n_units) && ok; ++round) {
+      const int u = unit_of_round(round, n_units);
+      if (u < 0) continue;
+      const KvUnit w = kv_unit(u, p);
+      const int row0 = w.blk * kT;
+      for (int i = 0; i < w.n_iter; ++i, ++it) {
+        ok = mbar_wait(bar(C::s_full), it & 1, abortp);
+        // the query columns' statistics landed with the streamed tiles: observe that barrier
+        // directly (it completed before the products this warp was woken by were issued)
+        if (ok) ok = mbar_wait(bar(C::str_full + it % C::kStages), (it / C::kStages) & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const int col0 = (w.lo + i % w.per_head) * kT;  // first query of the score columns
+        // under the causal mask a key row keeps the query columns with query >= key
+        const int c_first = p.causal ? row0 + r - col0 : 0;
+        const bool masked = __any_sync(0xffffffffu, c_first > 0);
+        const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
+                                                             (it % C::kStages) * C::kStatBytes);
+        const float* nd_col = nl_col + kT;
+        // This warp's two 32-column chunks of S^T and dP^T go to registers first.  bf16 P^T / dS^T of
+        // chunk c land on columns [16 c, 16 c + 16) of S^T / dP^T: the first half's results fall on its
+        // own chunk 0, the second half's on chunk 1 of the first half, which says on the pair barrier
+        // that it has read it; the second half passes that barrier before its first store.
+        uint32_t sr2[2][32], dp2[2][32];
 #pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
-        tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
-      }
-      tmem_wait_ld();
-#pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        tmem_ld_ready(sr2[step]);
-        tmem_ld_ready(dp2[step]);
-      }
-      if (half == 0) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(C::pair + quarter));
-      }
-#pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        const int c = 2 * half + step;
-        uint32_t(&sr)[32] = sr2[step];
-        uint32_t(&dp)[32] = dp2[step];
-        if (masked) {
-#pragma unroll
-          for (int x = 0; x < 32; ++x)
-            if (c * 32 + x < c_first || c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
+        for (int step = 0; step < 2; ++step) {
+          tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
+          tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
         }
-        uint32_t pk_p[16], pk_s[16];
+        tmem_wait_ld();
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          uint64_t nl2, nd2;
-          if (kMode == 0) {
+        for (int step = 0; step < 2; ++step) {
+          tmem_ld_ready(sr2[step]);
+          tmem_ld_ready(dp2[step]);
+        }
+        if (half == 0) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::pair + quarter));
+        }
+#pragma unroll
+        for (int step = 0; step < 2; ++step) {
+          const int c = 2 * half + step;
+          uint32_t(&sr)[32] = sr2[step];
+          uint32_t(&dp)[32] = dp2[step];
+          if (masked) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              if (c * 32 + x < c_first) sr[x] = 0xff800000u;  // -inf: P = 0
+          }
+          uint32_t pk_p[16], pk_s[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
             // statistics of the two query columns (every lane reads the same addresses)
             const float2 a = *reinterpret_cast<const float2*>(nl_col + c * 32 + 2 * x);
             const float2 d = *reinterpret_cast<const float2*>(nd_col + c * 32 + 2 * x);
-            nl2 = pack_f32x2(a.x, a.y);
-            nd2 = pack_f32x2(d.x, d.y);
-          } else {
-            nl2 = pack_f32x2(nl_row, nl_row);
-            nd2 = pack_f32x2(nd_row, nd_row);
+            const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, pack_f32x2(a.x, a.y));
+            float t0, t1;
+            unpack_f32x2(t2, t0, t1);
+            const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+            const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, pack_f32x2(d.x, d.y));
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
+            pk_p[x] = pack_bf16x2(p0, p1);
+            pk_s[x] = pack_bf16x2(d0, d1);
           }
-          const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, nl2);
-          float t0, t1;
-          unpack_f32x2(t2, t0, t1);
-          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-          const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, nd2);
-          float d0, d1;
-          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
-          pk_p[x] = pack_bf16x2(p0, p1);
-          pk_s[x] = pack_bf16x2(d0, d1);
+          if (step == 0 && half == 1) {
+            ok = mbar_wait(bar(C::pair + quarter), it & 1, abortp);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          tmem_st16(tS + c * 16, pk_p);
+          tmem_st16(tDP + c * 16, pk_s);
         }
-        if (step == 0 && half == 1) {
-          ok = mbar_wait(bar(C::pair + quarter), i & 1, abortp);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        if (kMode == 0) tmem_st16(tS + c * 16, pk_p);
-        tmem_st16(tDP + c * 16, pk_s);
+        if (!ok) break;
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::p_full));
       }
       if (!ok) break;
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::p_full));
-    }
 
-    // epilogue: accumulators -> bf16 -> global, one row per thread
-    if (ok && n_iter > 0) {
-      ok = mbar_wait(bar(C::acc_full), 0, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
+      // epilogue: dK and dV -> bf16 -> global, one key row per thread, half of the columns per warp
+      // of the pair; keys that no query sees get zeros without touching tensor memory
+      if (w.n_iter > 0) {
+        ok = mbar_wait(bar(C::acc_full), rc & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
       const int row = row0 + r;
-      const bool row_ok = row < (kMode == 0 ? p.kv_seq : p.q_seq);
+      const bool row_ok = row < p.kv_seq;
 #pragma unroll
-      for (int which = 0; which < (kMode == 0 ? 2 : 1); ++which) {
+      for (int which = 0; which < 2; ++which) {
         const uint32_t tA = tmem + lane_addr + (which ? C::kTmemAcc2 : C::kTmemAcc1);
         const int64_t* st = which ? p.out2_stride : p.out1_stride;
-        __nv_bfloat16* orow = (which ? p.out2 : p.out1) + b * st[0] + head * st[1] + (int64_t)row * st[2];
+        __nv_bfloat16* orow = (which ? p.out2 : p.out1) + w.b * st[0] + w.head * st[1] + (int64_t)row * st[2];
 #pragma unroll
         for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t o[32];
-          if (n_iter > 0) {
+          if (w.n_iter > 0) {
             tmem_ld32(tA + c * 32, o);
             tmem_wait_ld();
             tmem_ld_ready(o);
           } else {
 #pragma unroll
-            for (int x = 0; x < 32; ++x) o[x] = 0u;  // keys no query sees: zero gradient
+            for (int x = 0; x < 32; ++x) o[x] = 0u;
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -391,7 +415,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
           }
         }
       }
-      tc_fence_before();
+      if (w.n_iter > 0) {
+        // the accumulators are in registers / memory: the next unit may overwrite them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::acc_free));
+        ++rc;
+      }
     }
   }
 
@@ -417,8 +447,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_res1, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------------------------
-// dQ kernel with the score products running ahead of the elementwise step.
-// One CTA per 128 query rows of a (batch, query head): Q and dO stay in shared memory, K streams
+// dQ kernel with the score products running ahead of the elementwise step, persistent like the
+// dK/dV kernel.  One work unit = 128 query rows of a (batch, query head), the units with the most key
+// blocks first: Q and dO stay in shared memory (the next unit's are fetched once the unit's last
+// score products have read them), K streams
 // through a 3-stage ring and V through a 2-stage ring.  dS does not overlay dP here: tensor memory
 // has 128 columns to spare next to S, dP and dQ, enough for two bf16 dS buffers.  S and dP may
 // therefore be overwritten as soon as the elementwise warps hold them in registers, so
@@ -443,13 +475,29 @@ struct DqCfg {
   static constexpr int sdp_free = s_full + 1;            // S and dP are in registers (8 warp arrivals)
   static constexpr int p_full = sdp_free + 1;            // [2] dS buffer written (8 warp arrivals), alternating
   static constexpr int acc_full = p_full + 2;
-  static constexpr int kNumBars = acc_full + 1;
+  static constexpr int res_empty = acc_full + 1;         // the unit's last score products have read Q and dO
+  static constexpr int acc_free = res_empty + 1;         // the epilogue has read dQ (8 warp arrivals)
+  static constexpr int kNumBars = acc_free + 1;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc = 256, kTmemDS = 384;  // dS: 2 x 64 columns
   static_assert(256 + D + 128 <= 512, "tensor memory budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
+
+struct QUnit {
+  int blk, head, b, n_iter;  // key blocks 0 .. n_iter-1
+};
+__device__ __forceinline__ QUnit q_unit(int u, const BwdParams& p) {
+  QUnit w;
+  const int lvl = u / (p.n_head * p.batch);
+  const int rem = u - lvl * p.n_head * p.batch;
+  w.head = rem % p.n_head;
+  w.b = rem / p.n_head;
+  w.blk = p.n_qblk - 1 - lvl;
+  w.n_iter = p.causal ? min(p.n_kblk, w.blk + 1) : p.n_kblk;
+  return w;
+}
 
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -466,20 +514,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t sBar = base + C::kBarOff;
   auto bar = [&](int i) { return sBar + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // the query blocks with the most key blocks (the last ones under a causal mask) come first
-  const int lvl = blockIdx.x / (p.n_head * p.batch);
-  const int rem = blockIdx.x - lvl * p.n_head * p.batch;
-  const int head = rem % p.n_head, b = rem / p.n_head;
-  const int blk = p.n_qblk - 1 - lvl;
-  const int row0 = blk * kT;
-  const int hkv = head / p.group;
-  const int n_iter = p.causal ? min(p.n_kblk, blk + 1) : p.n_kblk;  // key blocks 0 .. n_iter-1
+  const int n_units = p.n_qblk * p.n_head * p.batch;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int i = 0; i < C::kNumBars; ++i)
-      mbar_init(bar(i), (i == C::sdp_free || i == C::p_full || i == C::p_full + 1) ? 8u : 1u);
+      mbar_init(bar(i), (i == C::sdp_free || i == C::p_full || i == C::p_full + 1 || i == C::acc_free) ? 8u : 1u);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
@@ -499,29 +539,38 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
-#pragma unroll
-      for (int kb = 0; kb < C::kBoxes; ++kb) {
-        tma_load_4d(base + C::kQ + kb * C::kBoxBytes, &tm_q, bar(C::res_full), kb * 64, row0, head, b);
-        tma_load_4d(base + C::kDO + kb * C::kBoxBytes, &tm_do, bar(C::res_full), kb * 64, row0, head, b);
-      }
       bool ok = true;
-      for (int i = 0; i < n_iter && ok; ++i) {
-        const int ks = i % C::kKStages, vs = i % C::kVStages;
-        if (i >= C::kKStages) ok = mbar_wait(bar(C::k_empty + ks), ((i / C::kKStages) - 1) & 1, abortp);
+      int it = 0, rc = 0;
+      for (int round = 0; round < rounds_of(n_units) && ok; ++round, ++rc) {
+        const int u = unit_of_round(round, n_units);
+        if (u < 0) break;  // only the last round can be short
+        const QUnit w = q_unit(u, p);
+        const int hkv = w.head / p.group;
+        if (rc > 0) ok = mbar_wait(bar(C::res_empty), (rc - 1) & 1, abortp);
         if (!ok) break;
-        mbar_expect_tx(bar(C::k_full + ks), C::kTileBytes);
+        mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
 #pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_load_4d(base + C::kK + ks * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(C::k_full + ks), kb * 64,
-                      i * kT, hkv, b);
-        if (i >= C::kVStages) ok = mbar_wait(bar(C::v_empty + vs), ((i / C::kVStages) - 1) & 1, abortp);
-        if (!ok) break;
-        mbar_expect_tx(bar(C::v_full + vs), C::kTileBytes);
+        for (int kb = 0; kb < C::kBoxes; ++kb) {
+          tma_load_4d(base + C::kQ + kb * C::kBoxBytes, &tm_q, bar(C::res_full), kb * 64, w.blk * kT, w.head, w.b);
+          tma_load_4d(base + C::kDO + kb * C::kBoxBytes, &tm_do, bar(C::res_full), kb * 64, w.blk * kT, w.head, w.b);
+        }
+        for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
+          const int ks = it % C::kKStages, vs = it % C::kVStages;
+          if (it >= C::kKStages) ok = mbar_wait(bar(C::k_empty + ks), ((it / C::kKStages) - 1) & 1, abortp);
+          if (!ok) break;
+          mbar_expect_tx(bar(C::k_full + ks), C::kTileBytes);
 #pragma unroll
-        for (int kb = 0; kb < C::kBoxes; ++kb)
-          tma_load_4d(base + C::kV + vs * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(C::v_full + vs), kb * 64,
-                      i * kT, hkv, b);
+          for (int kb = 0; kb < C::kBoxes; ++kb)
+            tma_load_4d(base + C::kK + ks * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(C::k_full + ks), kb * 64,
+                        i * kT, hkv, w.b);
+          if (it >= C::kVStages) ok = mbar_wait(bar(C::v_empty + vs), ((it / C::kVStages) - 1) & 1, abortp);
+          if (!ok) break;
+          mbar_expect_tx(bar(C::v_full + vs), C::kTileBytes);
+#pragma unroll
+          for (int kb = 0; kb < C::kBoxes; ++kb)
+            tma_load_4d(base + C::kV + vs * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(C::v_full + vs), kb * 64,
+                        i * kT, hkv, w.b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -529,10 +578,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (lane == 0) {
       const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP, tAcc = tmem + C::kTmemAcc;
       const uint32_t q_lo = umma_desc_lo(base + C::kQ, 16), do_lo = umma_desc_lo(base + C::kDO, 16);
-      auto scores = [&](int i) {  // S = Q K(i)^T, dP = dO V(i)^T; V(i) is free afterwards
-        const int ks = i % C::kKStages, vs = i % C::kVStages;
-        if (!mbar_wait(bar(C::k_full + ks), (i / C::kKStages) & 1, abortp)) return false;
-        if (!mbar_wait(bar(C::v_full + vs), (i / C::kVStages) & 1, abortp)) return false;
+      auto scores = [&](int g) {  // S = Q K^T, dP = dO V^T for streamed pair number g; V is free afterwards
+        const int ks = g % C::kKStages, vs = g % C::kVStages;
+        if (!mbar_wait(bar(C::k_full + ks), (g / C::kKStages) & 1, abortp)) return false;
+        if (!mbar_wait(bar(C::v_full + vs), (g / C::kVStages) & 1, abortp)) return false;
         tc_fence_after();
         issue_nt<D>(tS, q_lo, umma_desc_lo(base + C::kK + ks * C::kTileBytes, 16));
         issue_nt<D>(tDP, do_lo, umma_desc_lo(base + C::kV + vs * C::kTileBytes, 16));
@@ -540,24 +589,37 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         umma_commit(bar(C::v_empty + vs));
         return true;
       };
-      bool ok = mbar_wait(bar(C::res_full), 0, abortp);
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_iter && ok; ++i) {
-        if (i + 1 < n_iter) {
-          // S(i) and dP(i) are in the elementwise warps' registers: the next pair may overwrite them
-          ok = mbar_wait(bar(C::sdp_free), i & 1, abortp);
-          if (ok) ok = scores(i + 1);
+      bool ok = true;
+      int it = 0, rc = 0;
+      for (int round = 0; round < rounds_of(n_units) && ok; ++round, ++rc) {
+        const int u = unit_of_round(round, n_units);
+        if (u < 0) break;  // only the last round can be short
+        const QUnit w = q_unit(u, p);
+        ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
+        // S and dP of the previous unit's last pair must be in the elementwise warps' registers
+        if (ok && it > 0) ok = mbar_wait(bar(C::sdp_free), (it - 1) & 1, abortp);
+        if (ok) ok = scores(it);
+        if (ok && w.n_iter == 1) umma_commit(bar(C::res_empty));
+        for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
+          if (i + 1 < w.n_iter) {
+            // S(i) and dP(i) are in the elementwise warps' registers: the next pair may overwrite them
+            ok = mbar_wait(bar(C::sdp_free), it & 1, abortp);
+            if (ok) ok = scores(it + 1);
+            if (!ok) break;
+            if (i + 2 == w.n_iter) umma_commit(bar(C::res_empty));  // Q and dO are read by score products only
+          }
+          ok = mbar_wait(bar(C::p_full + (it & 1)), (it >> 1) & 1, abortp);
+          // the unit's first dQ product overwrites the accumulator the previous epilogue reads
+          if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
           if (!ok) break;
+          tc_fence_after();
+          const int ks = it % C::kKStages;
+          issue_acc<D>(tAcc, tmem + C::kTmemDS + (it & 1) * 64,
+                       umma_desc_lo(base + C::kK + ks * C::kTileBytes, C::kBoxBytes), i > 0);
+          umma_commit(bar(C::k_empty + ks));
         }
-        ok = mbar_wait(bar(C::p_full + (i & 1)), (i >> 1) & 1, abortp);
-        if (!ok) break;
-        tc_fence_after();
-        const int ks = i % C::kKStages;
-        issue_acc<D>(tAcc, tmem + C::kTmemDS + (i & 1) * 64,
-                     umma_desc_lo(base + C::kK + ks * C::kTileBytes, C::kBoxBytes), i > 0);
-        umma_commit(bar(C::k_empty + ks));
+        if (ok) umma_commit(bar(C::acc_full));
       }
-      if (ok) umma_commit(bar(C::acc_full));
     }
   } else if (warp >= 4) {
     // ------------------------------------------------ elementwise + epilogue
@@ -567,76 +629,81 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
     const uint64_t sl2x2 = pack_f32x2(p.sl2, p.sl2), scale2 = pack_f32x2(p.scale, p.scale);
-    const int64_t at = ((int64_t)b * p.n_head + head) * p.sq_pad + row0 + r;
-    const float nl_row = p.neg_lse2[at], nd_row = p.neg_delta_s[at];
-    const uint64_t nl2 = pack_f32x2(nl_row, nl_row), nd2 = pack_f32x2(nd_row, nd_row);
     bool ok = true;
-    for (int i = 0; i < n_iter; ++i) {
-      ok = mbar_wait(bar(C::s_full), i & 1, abortp);
+    int it = 0, rc = 0;
+    for (int round = 0; round < rounds_of(n_units) && ok; ++round, ++rc) {
+      const int u = unit_of_round(round, n_units);
+      if (u < 0) break;  // only the last round can be short
+      const QUnit w = q_unit(u, p);
+      const int row0 = w.blk * kT;
+      const int64_t at = ((int64_t)w.b * p.n_head + w.head) * p.sq_pad + row0 + r;
+      const float nl_row = p.neg_lse2[at], nd_row = p.neg_delta_s[at];
+      const uint64_t nl2 = pack_f32x2(nl_row, nl_row), nd2 = pack_f32x2(nd_row, nd_row);
+      for (int i = 0; i < w.n_iter; ++i, ++it) {
+        ok = mbar_wait(bar(C::s_full), it & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr2[2][32], dp2[2][32];
+#pragma unroll
+        for (int step = 0; step < 2; ++step) {
+          tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
+          tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
+        }
+        tmem_wait_ld();
+#pragma unroll
+        for (int step = 0; step < 2; ++step) {
+          tmem_ld_ready(sr2[step]);
+          tmem_ld_ready(dp2[step]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::sdp_free));
+
+        // keys this query row keeps under the causal mask: key <= query
+        const int c_limit = p.causal ? row0 + r - i * kT + 1 : kT;
+        const bool masked = __any_sync(0xffffffffu, c_limit < kT);
+        const uint32_t tDS = tmem + lane_addr + C::kTmemDS + (it & 1) * 64;
+#pragma unroll
+        for (int step = 0; step < 2; ++step) {
+          const int c = 2 * half + step;
+          uint32_t(&sr)[32] = sr2[step];
+          uint32_t(&dp)[32] = dp2[step];
+          if (masked) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              if (c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
+          }
+          uint32_t pk_s[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, nl2);
+            float t0, t1;
+            unpack_f32x2(t2, t0, t1);
+            const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+            const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, nd2);
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
+            pk_s[x] = pack_bf16x2(d0, d1);
+          }
+          tmem_st16(tDS + c * 16, pk_s);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::p_full + (it & 1)));
+      }
+      if (!ok) break;
+
+      // epilogue: dQ -> bf16 -> global, one row per thread, half of the columns per warp of the pair
+      ok = mbar_wait(bar(C::acc_full), rc & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after();
-      uint32_t sr2[2][32], dp2[2][32];
-#pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
-        tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
-      }
-      tmem_wait_ld();
-#pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        tmem_ld_ready(sr2[step]);
-        tmem_ld_ready(dp2[step]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::sdp_free));
-
-      // keys this query row keeps under the causal mask: key <= query
-      const int c_limit = p.causal ? row0 + r - i * kT + 1 : kT;
-      const bool masked = __any_sync(0xffffffffu, c_limit < kT);
-      const uint32_t tDS = tmem + lane_addr + C::kTmemDS + (i & 1) * 64;
-#pragma unroll
-      for (int step = 0; step < 2; ++step) {
-        const int c = 2 * half + step;
-        uint32_t(&sr)[32] = sr2[step];
-        uint32_t(&dp)[32] = dp2[step];
-        if (masked) {
-#pragma unroll
-          for (int x = 0; x < 32; ++x)
-            if (c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
-        }
-        uint32_t pk_s[16];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, nl2);
-          float t0, t1;
-          unpack_f32x2(t2, t0, t1);
-          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-          const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, nd2);
-          float d0, d1;
-          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
-          pk_s[x] = pack_bf16x2(d0, d1);
-        }
-        tmem_st16(tDS + c * 16, pk_s);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::p_full + (i & 1)));
-    }
-
-    // epilogue: dQ -> bf16 -> global, one row per thread, half of the columns per warp of the pair
-    if (ok) {
-      ok = mbar_wait(bar(C::acc_full), 0, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
       tc_fence_after();
       const int row = row0 + r;
       const bool row_ok = row < p.q_seq;
       const uint32_t tA = tmem + lane_addr + C::kTmemAcc;
-      __nv_bfloat16* orow = p.out1 + b * p.out1_stride[0] + head * p.out1_stride[1] + (int64_t)row * p.out1_stride[2];
+      __nv_bfloat16* orow = p.out1 + w.b * p.out1_stride[0] + w.head * p.out1_stride[1] + (int64_t)row * p.out1_stride[2];
 #pragma unroll
       for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t o[32];
@@ -653,7 +720,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = wv;
         }
       }
+      // dQ is in registers / memory: the next unit may overwrite the accumulator
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::acc_free));
     }
   }
 
@@ -714,20 +784,6 @@ bwd_rowstats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __
   }
 }
 
-template <int D, int kMode>
-int set_smem_attr() {
-  static std::atomic<bool> attr_set[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
-  if (!attr_set[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_kernel<D, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)BCfg<D>::kSmemBytes);
-    if (e != cudaSuccess) return (int)e;
-    attr_set[dev].store(true, std::memory_order_release);
-  }
-  return 0;
-}
-
 template <int D>
 int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStream_t st) {
   using C = BCfg<D>;
@@ -743,19 +799,20 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
   if ((rc = make_tile_map(&tk, a.k, a.batch, a.n_kv_head, a.kv_seq, D, a.k_stride))) return rc;
   if ((rc = make_tile_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
   if ((rc = make_tile_map(&tdo, a.d_o, a.batch, a.n_head, a.q_seq, D, a.do_stride))) return rc;
-  if ((rc = set_smem_attr<D, 0>())) return rc;
   {
     static std::atomic<bool> attr_set[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
     if (!attr_set[dev].load(std::memory_order_acquire)) {
-      cudaError_t e = cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)DqCfg<D>::kSmemBytes);
+      cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)C::kSmemBytes);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)DqCfg<D>::kSmemBytes);
       if (e != cudaSuccess) return (int)e;
       attr_set[dev].store(true, std::memory_order_release);
     }
   }
-
   {
     constexpr int kLanes = D / 8;
     const int64_t threads = padded_rows * kLanes;
@@ -787,6 +844,13 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
   p.sl2 = scale * kLog2e;
   p.status = status;
 
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
   const long long grid_kv = (long long)n_kblk * a.n_kv_head * a.batch;
   const long long grid_q = (long long)n_qblk * a.n_head * a.batch;
   if (grid_kv > 0x7fffffffLL || grid_q > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
@@ -797,7 +861,7 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
     p.out1_stride[i] = a.dk_stride[i];
     p.out2_stride[i] = a.dv_stride[i];
   }
-  bwd_kernel<D, 0><<<(unsigned)grid_kv, kBwdThreads, C::kSmemBytes, st>>>(tk, tv, tq, tdo, p);
+  bwd_dkdv_kernel<D><<<(unsigned)std::min<long long>(grid_kv, sms), kBwdThreads, C::kSmemBytes, st>>>(tk, tv, tq, tdo, p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
@@ -808,7 +872,7 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
     p.out1_stride[i] = a.dq_stride[i];
     p.out2_stride[i] = 0;
   }
-  bwd_dq_kernel<D><<<(unsigned)grid_q, kBwdThreads, DqCfg<D>::kSmemBytes, st>>>(tq, tdo, tk, tv, p);
+  bwd_dq_kernel<D><<<(unsigned)std::min<long long>(grid_q, sms), kBwdThreads, DqCfg<D>::kSmemBytes, st>>>(tq, tdo, tk, tv, p);
   count_launch();
   return (int)cudaGetLastError();
 }
