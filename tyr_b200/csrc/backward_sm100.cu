@@ -63,11 +63,12 @@ struct BCfg {
   static constexpr int s_full = 5;                     // S and dP in tensor memory
   static constexpr int p_full = 6;                     // P / dS written (one arrival per elementwise warp)
   static constexpr int acc_full = 7;                   // last accumulating product done
-  static constexpr int pair = 8;                       // [4] per lane quarter: the warp of the first column half
-                                                       //     has read the columns the other warp's P / dS overwrite
+  static constexpr int pair = 8;                       // [4] per lane quarter: both warps hold their score columns
+                                                       //     in registers (P / dS overwrite each other's columns)
   static constexpr int res_empty = 12;                 // the unit's last score products have read K and V
   static constexpr int acc_free = 13;                  // the epilogue has read dK and dV (8 warp arrivals)
-  static constexpr int kNumBars = 14;
+  static constexpr int p_half = 14;                    // P / dS of score columns 0..63 written (8 warp arrivals)
+  static constexpr int kNumBars = 15;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc1 = 256, kTmemAcc2 = 256 + D;
@@ -107,13 +108,17 @@ __device__ __forceinline__ void issue_nt(uint32_t d_tmem, uint32_t a_lo, uint32_
     }
   }
 }
-// accumulating product: D[128 x D] (+)= A[128 x 128 bf16, tensor memory] B[128 x D], B MN-major
+// accumulating product: D[128 x D] (+)= A[128 x 128 bf16, tensor memory] B[128 x D], B MN-major.
+// `part` 0 / 1: the first / second 64 of the 128 reduction steps only; -1: all of them.
 template <int D>
-__device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool accumulate) {
+__device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool accumulate,
+                                          int part = -1) {
   constexpr uint32_t idesc = umma_idesc_bf16(kT, D, true);
   asm volatile("" : "+r"(b_lo), "+r"(a_tmem));
+  const int k0 = part == 1 ? kT / 32 : 0, k1 = part == 0 ? kT / 32 : kT / 16;
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
+    if (kk < k0 || kk >= k1) continue;
     // 16 rows of B = two 8-row groups of the tile; 16 bf16 of A = 8 TMEM columns
     if (kk == 0)
       umma_ts_lo<-1>(d_tmem, a_tmem, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u);
@@ -176,7 +181,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int i = 0; i < C::kNumBars; ++i)
-      mbar_init(bar(i), (i == C::p_full || i == C::acc_free) ? 8u : 1u);
+      mbar_init(bar(i), (i == C::p_full || i == C::p_half || i == C::acc_free) ? 8u
+                        : (i >= C::pair && i < C::pair + 4) ? 2u : 1u);
     mbar_fence_init();
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -263,14 +269,22 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           const int s = it % C::kStages;
           const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
-          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
+          // the first 64 query columns of P^T / dS^T are written while the second 64 are still
+          // being formed: their share of the accumulating products starts now
+          ok = mbar_wait(bar(C::p_half), it & 1, abortp);
           // the unit's first accumulating products overwrite dK / dV: the previous unit's
           // epilogue must have read them
           if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          issue_acc<D>(tA1, tDP, umma_desc_lo(t1, C::kBoxBytes), i > 0);                    // dK += dS^T Q
-          issue_acc<D>(tA2, tS, umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes), i > 0);     // dV += P^T dO
+          const uint32_t q_mn = umma_desc_lo(t1, C::kBoxBytes), do_mn = umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes);
+          issue_acc<D>(tA1, tDP, q_mn, i > 0, 0);   // dK += dS^T Q
+          issue_acc<D>(tA2, tS, do_mn, i > 0, 0);   // dV += P^T dO
+          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc<D>(tA1, tDP, q_mn, true, 1);
+          issue_acc<D>(tA2, tS, do_mn, true, 1);
           umma_commit(bar(C::str_empty + s));
           if (i + 1 < w.n_iter) {
             ok = scores(it + 1);
@@ -314,15 +328,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
                                                              (it % C::kStages) * C::kStatBytes);
         const float* nd_col = nl_col + kT;
-        // This warp's two 32-column chunks of S^T and dP^T go to registers first.  bf16 P^T / dS^T of
-        // chunk c land on columns [16 c, 16 c + 16) of S^T / dP^T: the first half's results fall on its
-        // own chunk 0, the second half's on chunk 1 of the first half, which says on the pair barrier
-        // that it has read it; the second half passes that barrier before its first store.
+        // This warp's two 32-column chunks of S^T and dP^T go to registers first: chunk `half` of the
+        // first 64 query columns and chunk 2 + `half` of the second 64.  bf16 P^T / dS^T of chunk c
+        // land on columns [16 c, 16 c + 16) of S^T / dP^T, i.e. on chunks 0 and 1, which belong to
+        // different warps of the pair: the two meet once both hold their columns in registers.
         uint32_t sr2[2][32], dp2[2][32];
 #pragma unroll
         for (int step = 0; step < 2; ++step) {
-          tmem_ld32(tS + (2 * half + step) * 32, sr2[step]);
-          tmem_ld32(tDP + (2 * half + step) * 32, dp2[step]);
+          tmem_ld32(tS + (2 * step + half) * 32, sr2[step]);
+          tmem_ld32(tDP + (2 * step + half) * 32, dp2[step]);
         }
         tmem_wait_ld();
 #pragma unroll
@@ -330,14 +344,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           tmem_ld_ready(sr2[step]);
           tmem_ld_ready(dp2[step]);
         }
-        if (half == 0) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(C::pair + quarter));
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::pair + quarter));
 #pragma unroll
         for (int step = 0; step < 2; ++step) {
-          const int c = 2 * half + step;
+          const int c = 2 * step + half;
           uint32_t(&sr)[32] = sr2[step];
           uint32_t(&dp)[32] = dp2[step];
           if (masked) {
@@ -361,7 +373,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
             pk_p[x] = pack_bf16x2(p0, p1);
             pk_s[x] = pack_bf16x2(d0, d1);
           }
-          if (step == 0 && half == 1) {
+          if (step == 0) {
             ok = mbar_wait(bar(C::pair + quarter), it & 1, abortp);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -369,12 +381,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           }
           tmem_st16(tS + c * 16, pk_p);
           tmem_st16(tDP + c * 16, pk_s);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(step == 0 ? C::p_half : C::p_full));
         }
         if (!ok) break;
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(C::p_full));
       }
       if (!ok) break;
 
