@@ -303,6 +303,15 @@ def run_profile(args):
         o, lse = torch.empty_like(q), torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
         step = lambda: tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse)  # noqa: E731
         work, unit = w.flops / 1e12, "TFLOP/s"
+    elif args.profile == "backward":
+        w = W.WORKLOADS[args.workload]
+        q, k, v = (t.to(dev) for t in W.make_prefill(w))
+        g = torch.Generator(device=dev).manual_seed(w.seed + 100)
+        d_o = torch.randn(q.shape, device=dev, generator=g).bfloat16()
+        o, lse = tnn.attentionFwd(q, k, v, is_causal=w.causal)
+        ws = torch.empty(2 * lse.numel(), device=dev)
+        step = lambda: tnn.attentionBwd(q, k, v, o, lse, d_o, is_causal=w.causal, workspace=ws)  # noqa: E731
+        work, unit = 2.5 * w.flops / 1e12, "TFLOP/s"
     else:
         w = W.WORKLOADS["qwen3_8b_decode"]
         q, ks, vs, lens = W.make_decode(w, batch=args.decode_batch, device=str(dev))
@@ -454,7 +463,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=[n for n, w in W.WORKLOADS.items() if w.kind == "prefill"])
     ap.add_argument("--no-others", action="store_true", help="skip the extra kernel-only workloads")
-    ap.add_argument("--profile", choices=["prefill", "decode"], default=None,
+    ap.add_argument("--profile", choices=["prefill", "backward", "decode"], default=None,
                     help="profiler-friendly run: only warm-up + steps of one kernel, no e2e/CPU legs")
     ap.add_argument("--decode-batch", type=int, default=None, help="sequences of the decode workload (profile runs)")
     args = ap.parse_args()
