@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 4
+#define TYR_ATTN_ABI_VERSION 5
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -270,6 +270,9 @@ typedef struct TyrAttnBackwardArgs {
   int32_t dtype;            /* TYR_ATTN_BF16 */
   int32_t is_causal;        /* key j hidden from query i when j > i, as in the forward */
   float scale;              /* <= 0: 1/sqrt(head_dim) */
+  int32_t window_size;      /* as in TyrAttnPrefillArgs: 0 => none; w > 0 => causal sliding window */
+  const uint8_t* key_mask;  /* as in TyrAttnPrefillArgs: NULL or DEVICE bytes [batch, kv_seq], 0 = padding key */
+  int64_t key_mask_stride;
 } TyrAttnBackwardArgs;
 
 uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, int32_t q_seq);

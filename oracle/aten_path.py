@@ -71,12 +71,18 @@ def sdpa_gqa_mask(q, k, v, padding_mask, dropout_p: float = 0.0, is_causal: bool
     return F.scaled_dot_product_attention(q, k, v, mask, dropout_p, False)
 
 
-def sdpa_gqa_backward(q, k, v, d_o, is_causal: bool = True):
+def sdpa_gqa_backward(q, k, v, d_o, is_causal: bool = True, window: int = 0, padding_mask=None):
     """Gradients LibTorch autograd gives the reference for its typed attention call:
     `output.backward(grad_output)` (cc/src/tyr.cpp:2111-2122) through lean_torch_sdpa_gqa
-    (cc/src/tyr.cpp:3913-3949, repeat_interleave included).  Returns (d_q, d_k, d_v)."""
+    (cc/src/tyr.cpp:3913-3949, repeat_interleave included), or through the windowed / padding-masked
+    entry points when `window` / `padding_mask` is given.  Returns (d_q, d_k, d_v)."""
     q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
-    out = sdpa_gqa(q, k, v, 0.0, is_causal, True)
+    if window:
+        out = sdpa_gqa_window(q, k, v, 0.0, is_causal, True, window)
+    elif padding_mask is not None:
+        out = sdpa_gqa_mask(q, k, v, padding_mask, 0.0, is_causal, True)
+    else:
+        out = sdpa_gqa(q, k, v, 0.0, is_causal, True)
     out.backward(d_o)
     return q.grad, k.grad, v.grad
 

@@ -207,9 +207,10 @@ int tyr_oracle_sdpa_online(const float* q, const float* k, const float* v, float
 /* Backward of the direct form in double precision.  One (batch, KV head) per task: dK and dV
  * of a KV head sum over the Hq / Hkv query heads that share it (the derivative of
  * repeat_interleave, cc/src/tyr.cpp:3931-3938).  Returns 0, or -1 on bad arguments. */
-int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, const float* d_o,
-                             float* d_q, float* d_k, float* d_v, int B, int Hq, int Hkv, int Sq,
-                             int Skv, int D, int is_causal, float scale) {
+static int sdpa_backward_direct(const float* q, const float* k, const float* v, const float* d_o,
+                                float* d_q, float* d_k, float* d_v, int B, int Hq, int Hkv, int Sq,
+                                int Skv, int D, int is_causal, float scale, int window,
+                                const uint8_t* key_mask) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || Hq % Hkv != 0) return -1;
   const int g = Hq / Hkv;
   const int64_t tasks = (int64_t)B * Hkv;
@@ -239,19 +240,21 @@ int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, con
             const float* qr = q + r * D;
             const float* gr = d_o + r * D;
             const int n = is_causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv; /* keys j <= i */
+            const int j0 = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0; /* i - j < window */
             double mx = -INFINITY, sum = 0.0, delta = 0.0;
-            for (int j = 0; j < n; ++j) {
+            for (int j = j0; j < n; ++j) {
               double dot = 0.0;
               for (int d = 0; d < D; ++d) dot += (double)qr[d] * (double)kb[(int64_t)j * D + d];
               p[j] = dot * (double)scale;
+              if (key_mask && key_mask[(int64_t)b * Skv + j] == 0) p[j] = -INFINITY; /* padding key */
               if (p[j] > mx) mx = p[j];
             }
-            for (int j = 0; j < n; ++j) {
-              p[j] = exp(p[j] - mx);
+            for (int j = j0; j < n; ++j) {
+              p[j] = (p[j] == -INFINITY) ? 0.0 : exp(p[j] - mx);
               sum += p[j];
             }
             for (int d = 0; d < D; ++d) o[d] = 0.0;
-            for (int j = 0; j < n; ++j) {
+            for (int j = j0; j < n; ++j) {
               p[j] /= sum; /* softmax row */
               double g_dot_v = 0.0;
               for (int d = 0; d < D; ++d) {
@@ -262,7 +265,7 @@ int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, con
             }
             for (int d = 0; d < D; ++d) delta += (double)gr[d] * o[d]; /* d = rowsum(dO * O) */
             for (int d = 0; d < D; ++d) dq[d] = 0.0;
-            for (int j = 0; j < n; ++j) {
+            for (int j = j0; j < n; ++j) {
               const double ds = (double)scale * p[j] * (dp[j] - delta);
               for (int d = 0; d < D; ++d) {
                 dv[(int64_t)j * D + d] += p[j] * (double)gr[d];         /* dV = P^T dO */
@@ -287,6 +290,22 @@ int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, con
     free(dq);
   }
   return failed ? -1 : 0;
+}
+
+int tyr_oracle_sdpa_backward(const float* q, const float* k, const float* v, const float* d_o,
+                             float* d_q, float* d_k, float* d_v, int B, int Hq, int Hkv, int Sq,
+                             int Skv, int D, int is_causal, float scale) {
+  return sdpa_backward_direct(q, k, v, d_o, d_q, d_k, d_v, B, Hq, Hkv, Sq, Skv, D, is_causal, scale, 0, NULL);
+}
+
+/* The same under the sliding-window mask (window > 0, always with the causal mask, cc/src/tyr.cpp:3986-3996)
+ * and / or the key padding mask (key_mask [B, Skv] bytes, 0 = padding key, cc/src/tyr.cpp:4063-4086). */
+int tyr_oracle_sdpa_backward_masked(const float* q, const float* k, const float* v, const float* d_o,
+                                    float* d_q, float* d_k, float* d_v, int B, int Hq, int Hkv, int Sq,
+                                    int Skv, int D, int is_causal, float scale, int window,
+                                    const uint8_t* key_mask) {
+  return sdpa_backward_direct(q, k, v, d_o, d_q, d_k, d_v, B, Hq, Hkv, Sq, Skv, D,
+                              (is_causal || window > 0) ? 1 : 0, scale, window, key_mask);
 }
 
 /* L = Lr + log(1 + exp(Lb - Lr));  O = Or*exp(Lr - L) + Ob*exp(Lb - L)

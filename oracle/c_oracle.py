@@ -37,6 +37,9 @@ def lib() -> ctypes.CDLL:
         L.tyr_oracle_sdpa_online.restype = ctypes.c_int
         L.tyr_oracle_sdpa_backward.argtypes = [f32p] * 7 + [ctypes.c_int] * 7 + [ctypes.c_float]
         L.tyr_oracle_sdpa_backward.restype = ctypes.c_int
+        L.tyr_oracle_sdpa_backward_masked.argtypes = ([f32p] * 7 + [ctypes.c_int] * 7 + [ctypes.c_float, ctypes.c_int,
+                                                      ctypes.POINTER(ctypes.c_uint8)])
+        L.tyr_oracle_sdpa_backward_masked.restype = ctypes.c_int
         L.tyr_oracle_merge2.argtypes = [f32p] * 6 + [ctypes.c_int64, ctypes.c_int]
         L.tyr_oracle_merge2.restype = None
         L.tyr_oracle_bf16_round.argtypes = [f32p, f32p, ctypes.c_int64]
@@ -62,8 +65,9 @@ def threads() -> int:
     return int(lib().tyr_oracle_threads())
 
 
-def sdpa_backward(q, k, v, d_o, is_causal: bool, scale: float | None = None):
-    """Gradients of `sdpa` for the cotangent d_o: (d_q [B,Hq,Sq,D], d_k, d_v [B,Hkv,Skv,D])."""
+def sdpa_backward(q, k, v, d_o, is_causal: bool, scale: float | None = None, window: int = 0, key_mask=None):
+    """Gradients of `sdpa` for the cotangent d_o: (d_q [B,Hq,Sq,D], d_k, d_v [B,Hkv,Skv,D]).
+    `window` / `key_mask` as in `sdpa`."""
     q, k, v, d_o = _c(q), _c(k), _c(v), _c(d_o)
     B, Hq, Sq, D = q.shape
     _, Hkv, Skv, _ = k.shape
@@ -71,8 +75,17 @@ def sdpa_backward(q, k, v, d_o, is_causal: bool, scale: float | None = None):
     if scale is None:
         scale = 1.0 / float(np.sqrt(D))
     d_q, d_k, d_v = np.empty_like(q), np.empty_like(k), np.empty_like(v)
-    rc = lib().tyr_oracle_sdpa_backward(_p(q), _p(k), _p(v), _p(d_o), _p(d_q), _p(d_k), _p(d_v), B, Hq, Hkv,
-                                        Sq, Skv, D, int(bool(is_causal)), scale)
+    if window or key_mask is not None:
+        km = None
+        if key_mask is not None:
+            km = np.ascontiguousarray(np.asarray(key_mask) != 0, dtype=np.uint8)
+            assert km.shape == (B, Skv)
+        rc = lib().tyr_oracle_sdpa_backward_masked(
+            _p(q), _p(k), _p(v), _p(d_o), _p(d_q), _p(d_k), _p(d_v), B, Hq, Hkv, Sq, Skv, D, int(bool(is_causal)),
+            scale, int(window), km.ctypes.data_as(ctypes.POINTER(ctypes.c_uint8)) if km is not None else None)
+    else:
+        rc = lib().tyr_oracle_sdpa_backward(_p(q), _p(k), _p(v), _p(d_o), _p(d_q), _p(d_k), _p(d_v), B, Hq, Hkv,
+                                            Sq, Skv, D, int(bool(is_causal)), scale)
     if rc != 0:
         raise ValueError("tyr_oracle_sdpa_backward rejected its arguments")
     return d_q, d_k, d_v

@@ -140,3 +140,58 @@ def test_full_headline_shape_properties():
     rhs = (d_k.float() * k.float()).sum(dim=(2, 3))
     scale = (d_q.float().abs() * q.float().abs()).sum(dim=(2, 3)).view(B, Hkv, Hq // Hkv).sum(-1)
     assert ((lhs - rhs).abs() / scale).max().item() < 2e-3
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,window", [(1, 2, 1, 200, 64, 7), (2, 2, 2, 400, 128, 140),
+                                                 (1, 4, 2, 1000, 128, 300), (1, 1, 1, 130, 64, 2)])
+def test_sliding_window_backward(B, Hq, Hkv, S, D, window):
+    """Backward of the windowed call (lean_torch_sdpa_gqa_window under autograd) against the oracle."""
+    from tyr_b200 import nn as tnn
+    g = torch.Generator().manual_seed(S + window)
+    q, d_o = (torch.randn(B, Hq, S, D, generator=g).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, Hkv, S, D, generator=g).bfloat16() for _ in range(2))
+    want = c_oracle.sdpa_backward(*(t.float().numpy() for t in (q, k, v, d_o)), True, window=window)
+    qd, kd, vd, dd = (t.to(_dev()) for t in (q, k, v, d_o))
+    o, lse = tnn.attentionFwd(qd, kd, vd, window_size=window)
+    got = tnn.attentionBwd(qd, kd, vd, o, lse, dd, window_size=window)
+    torch.cuda.synchronize()
+    assert tnn.device_status(0, True) == 0
+    for gt, w, key in zip(got, want, ("d_q", "d_k", "d_v")):
+        _close(gt, w, key)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_padding_mask_backward(causal):
+    """Backward of the padding-masked call against the oracle; padding keys get exactly zero gradient."""
+    from tyr_b200 import nn as tnn
+    g = torch.Generator().manual_seed(41)
+    B, Hq, Hkv, S, D = 3, 4, 2, 300, 128
+    q, d_o = (torch.randn(B, Hq, S, D, generator=g).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, Hkv, S, D, generator=g).bfloat16() for _ in range(2))
+    m = torch.ones(B, S, dtype=torch.uint8)
+    m[0, 170:] = 0          # right padding
+    m[1, 20:45] = 0         # a hole
+    m[1, 128:260] = 0       # a whole tile and more
+    want = c_oracle.sdpa_backward(*(t.float().numpy() for t in (q, k, v, d_o)), causal, key_mask=m.numpy())
+    qd, kd, vd, dd, md = (t.to(_dev()) for t in (q, k, v, d_o, m))
+    o, lse = tnn.attentionFwd(qd, kd, vd, is_causal=causal, key_mask=md)
+    got = tnn.attentionBwd(qd, kd, vd, o, lse, dd, is_causal=causal, key_mask=md)
+    torch.cuda.synchronize()
+    assert tnn.device_status(0, True) == 0
+    for gt, w, key in zip(got, want, ("d_q", "d_k", "d_v")):
+        _close(gt, w, key)
+    assert torch.count_nonzero(got[1][0, :, 170:]) == 0 and torch.count_nonzero(got[2][1, :, 128:260]) == 0
+
+
+def test_window_of_one_is_closed_form():
+    """window_size = 1: every query sees only its own key, P = 1, so dV_j is the sum of the group's dO_j exactly
+    and dQ, dK vanish (up to the bf16 rounding of O inside delta)."""
+    from tyr_b200 import nn as tnn
+    g = torch.Generator().manual_seed(51)
+    q, d_o = (torch.randn(1, 2, 130, 64, generator=g).bfloat16().to(_dev()) for _ in range(2))
+    k, v = (torch.randn(1, 1, 130, 64, generator=g).bfloat16().to(_dev()) for _ in range(2))
+    o, lse = tnn.attentionFwd(q, k, v, window_size=1)
+    d_q, d_k, d_v = tnn.attentionBwd(q, k, v, o, lse, d_o, window_size=1)
+    torch.cuda.synchronize()
+    assert torch.equal(d_v, (d_o[:, 0].float() + d_o[:, 1].float()).bfloat16()[:, None])
+    assert d_q.float().abs().max().item() < 0.1 and d_k.float().abs().max().item() < 0.1

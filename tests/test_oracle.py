@@ -246,3 +246,25 @@ def test_backward_of_a_single_key_is_closed_form():
     np.testing.assert_allclose(d_q, 0, atol=1e-6)
     np.testing.assert_allclose(d_k, 0, atol=1e-6)
     np.testing.assert_allclose(d_v[0, 0, 0], d_o.sum(axis=(0, 1, 2)), rtol=1e-5, atol=1e-6)
+
+
+def test_masked_backward_oracle_matches_autograd():
+    """Sliding-window and padding-mask backward of the C oracle against torch autograd through the restated
+    lean_torch_sdpa_gqa_window / lean_torch_sdpa_gqa_mask."""
+    g = torch.Generator().manual_seed(31)
+    B, Hq, Hkv, S, D = 2, 4, 2, 45, 16
+    q, d_o = (torch.randn(B, Hq, S, D, generator=g) for _ in range(2))
+    k, v = (torch.randn(B, Hkv, S, D, generator=g) for _ in range(2))
+    want = aten_path.sdpa_gqa_backward(q, k, v, d_o, True, window=7)
+    got = c_oracle.sdpa_backward(q.numpy(), k.numpy(), v.numpy(), d_o.numpy(), True, window=7)
+    for a, b in zip(got, want):
+        np.testing.assert_allclose(a, b.numpy(), rtol=0, atol=2e-5)
+    m = torch.ones(B, S)
+    m[0, 30:] = 0
+    m[1, 5:12] = 0
+    for causal in (True, False):
+        want = aten_path.sdpa_gqa_backward(q, k, v, d_o, causal, padding_mask=m)
+        got = c_oracle.sdpa_backward(q.numpy(), k.numpy(), v.numpy(), d_o.numpy(), causal, key_mask=m.numpy())
+        for a, b in zip(got, want):
+            np.testing.assert_allclose(a, b.numpy(), rtol=0, atol=2e-5)
+        assert np.count_nonzero(got[1][0, :, 30:]) == 0 and np.count_nonzero(got[2][1, :, 5:12]) == 0

@@ -71,6 +71,7 @@ class BackwardArgs(ctypes.Structure):
         ("o_stride", c_i64 * 3), ("do_stride", c_i64 * 3),
         ("dq_stride", c_i64 * 3), ("dk_stride", c_i64 * 3), ("dv_stride", c_i64 * 3),
         ("dtype", c_i32), ("is_causal", c_i32), ("scale", c_f32),
+        ("window_size", c_i32), ("key_mask", vp), ("key_mask_stride", c_i64),
     ]
 
 

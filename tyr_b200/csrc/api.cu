@@ -250,6 +250,9 @@ int tyr_b200_attn_backward(const TyrAttnBackwardArgs* a, void* stream) {
   if (a->dtype != TYR_ATTN_BF16) return -TYR_ATTN_ERR_DTYPE;
   if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
   if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
+  // the windowed call has one sequence length (cc/src/tyr.cpp:3953-3965)
+  if (a->window_size < 0 || (a->window_size > 0 && a->q_seq != a->kv_seq)) return -TYR_ATTN_ERR_SHAPE;
+  if (a->key_mask && a->batch > 1 && a->key_mask_stride < a->kv_seq) return -TYR_ATTN_ERR_SHAPE;
   const void* ptrs[8] = {a->q, a->k, a->v, a->o, a->d_o, a->d_q, a->d_k, a->d_v};
   const int64_t* strides[8] = {a->q_stride, a->k_stride, a->v_stride, a->o_stride,
                                a->do_stride, a->dq_stride, a->dk_stride, a->dv_stride};

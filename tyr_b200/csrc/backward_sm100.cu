@@ -84,6 +84,9 @@ struct BwdParams {
   const float* neg_delta_s;  // [batch * n_head, sq_pad]  -delta * scale;  0 on padding rows
   int sq_pad;
   int batch, q_seq, kv_seq, n_head, n_kv_head, group, causal;
+  int window;               // 0: none; w > 0: key j visible to query i only while i - j < w (with causal)
+  const uint8_t* key_mask;  // [batch, kv_seq] bytes, 0 = padding key no query sees; or null
+  int64_t key_mask_stride;
   int n_qblk, n_kblk;
   float sl2, scale;
   int* status;
@@ -152,7 +155,9 @@ __device__ __forceinline__ KvUnit kv_unit(int u, const BwdParams& p) {
   w.b = rem / p.n_kv_head;
   w.blk = lvl;
   w.lo = p.causal ? min(w.blk, p.n_qblk) : 0;
-  w.per_head = p.n_qblk - w.lo;
+  int hi = p.n_qblk;  // one past the last query block that sees a key of the unit
+  if (p.window > 0) hi = min(hi, (w.blk * kT + kT - 1 + p.window - 1) / kT + 1);
+  w.per_head = max(hi - w.lo, 0);
   w.n_iter = w.per_head * p.group;
   return w;
 }
@@ -323,8 +328,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         tc_fence_after();
         const int col0 = (w.lo + i % w.per_head) * kT;  // first query of the score columns
         // under the causal mask a key row keeps the query columns with query >= key
-        const int c_first = p.causal ? row0 + r - col0 : 0;
-        const bool masked = __any_sync(0xffffffffu, c_first > 0);
+        int c_first = p.causal ? row0 + r - col0 : 0;
+        // sliding window: the key also drops out for queries with query - key >= window
+        const int c_limit = p.window > 0 ? row0 + r - col0 + p.window : kT;
+        // a padding key sees no query at all
+        if (p.key_mask != nullptr && (row0 + r >= p.kv_seq || p.key_mask[w.b * p.key_mask_stride + row0 + r] == 0))
+          c_first = kT;
+        const bool masked = __any_sync(0xffffffffu, c_first > 0 || c_limit < kT);
         const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
                                                              (it % C::kStages) * C::kStatBytes);
         const float* nd_col = nl_col + kT;
@@ -355,7 +365,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           if (masked) {
 #pragma unroll
             for (int x = 0; x < 32; ++x)
-              if (c * 32 + x < c_first) sr[x] = 0xff800000u;  // -inf: P = 0
+              if (c * 32 + x < c_first || c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
           }
           uint32_t pk_p[16], pk_s[16];
 #pragma unroll
@@ -498,7 +508,9 @@ struct DqCfg {
 };
 
 struct QUnit {
-  int blk, head, b, n_iter;  // key blocks 0 .. n_iter-1
+  int blk, head, b;
+  int lo;      // first key block a row of the unit sees (> 0 only under a sliding window)
+  int n_iter;  // key blocks lo .. lo + n_iter - 1
 };
 __device__ __forceinline__ QUnit q_unit(int u, const BwdParams& p) {
   QUnit w;
@@ -507,7 +519,8 @@ __device__ __forceinline__ QUnit q_unit(int u, const BwdParams& p) {
   w.head = rem % p.n_head;
   w.b = rem / p.n_head;
   w.blk = p.n_qblk - 1 - lvl;
-  w.n_iter = p.causal ? min(p.n_kblk, w.blk + 1) : p.n_kblk;
+  w.lo = p.window > 0 ? max(w.blk * kT - p.window + 1, 0) / kT : 0;
+  w.n_iter = (p.causal ? min(p.n_kblk, w.blk + 1) : p.n_kblk) - w.lo;
   return w;
 }
 
@@ -574,14 +587,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
           for (int kb = 0; kb < C::kBoxes; ++kb)
             tma_load_4d(base + C::kK + ks * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(C::k_full + ks), kb * 64,
-                        i * kT, hkv, w.b);
+                        (w.lo + i) * kT, hkv, w.b);
           if (it >= C::kVStages) ok = mbar_wait(bar(C::v_empty + vs), ((it / C::kVStages) - 1) & 1, abortp);
           if (!ok) break;
           mbar_expect_tx(bar(C::v_full + vs), C::kTileBytes);
 #pragma unroll
           for (int kb = 0; kb < C::kBoxes; ++kb)
             tma_load_4d(base + C::kV + vs * C::kTileBytes + kb * C::kBoxBytes, &tm_v, bar(C::v_full + vs), kb * 64,
-                        i * kT, hkv, w.b);
+                        (w.lo + i) * kT, hkv, w.b);
         }
       }
     }
@@ -673,8 +686,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) mbar_arrive(bar(C::sdp_free));
 
         // keys this query row keeps under the causal mask: key <= query
-        const int c_limit = p.causal ? row0 + r - i * kT + 1 : kT;
-        const bool masked = __any_sync(0xffffffffu, c_limit < kT);
+        const int col0 = (w.lo + i) * kT;  // first key of the score columns
+        const int c_limit = p.causal ? row0 + r - col0 + 1 : kT;
+        // sliding window: keys with query - key >= window drop out
+        const int c_first = p.window > 0 ? row0 + r - p.window + 1 - col0 : 0;
+        // padding keys: lane l fetches the mask bytes of keys 2l, 2l+1 of this warp's 64 columns, two
+        // ballots spread them to every row; column j of the 64 is bit (j >> 1) of ballot (j & 1)
+        uint32_t vb[2] = {0xffffffffu, 0xffffffffu};
+        if (p.key_mask != nullptr) {
+          const uint8_t* mrow = p.key_mask + w.b * p.key_mask_stride + col0 + 64 * half;
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kk = 2 * lane + e;
+            vb[e] = __ballot_sync(0xffffffffu, (col0 + 64 * half + kk < p.kv_seq) && mrow[kk] != 0);
+          }
+        }
+        const bool masked = __any_sync(0xffffffffu, c_limit < kT || c_first > 0) || (vb[0] & vb[1]) != 0xffffffffu;
         const uint32_t tDS = tmem + lane_addr + C::kTmemDS + (it & 1) * 64;
 #pragma unroll
         for (int step = 0; step < 2; ++step) {
@@ -684,7 +711,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (masked) {
 #pragma unroll
             for (int x = 0; x < 32; ++x)
-              if (c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
+              if (c * 32 + x >= c_limit || c * 32 + x < c_first || !((vb[x & 1] >> ((32 * step + x) >> 1)) & 1u))
+                sr[x] = 0xff800000u;  // -inf: P = 0
           }
           uint32_t pk_s[16];
 #pragma unroll
@@ -849,7 +877,10 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
   p.n_head = a.n_head;
   p.n_kv_head = a.n_kv_head;
   p.group = a.n_head / a.n_kv_head;
-  p.causal = a.is_causal ? 1 : 0;
+  p.causal = (a.is_causal || a.window_size > 0) ? 1 : 0;
+  p.window = a.window_size > 0 ? a.window_size : 0;
+  p.key_mask = a.key_mask;
+  p.key_mask_stride = a.key_mask_stride;
   p.n_qblk = n_qblk;
   p.n_kblk = n_kblk;
   p.scale = scale;

@@ -108,7 +108,8 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
 
 def attentionBwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
                  d_o: torch.Tensor, is_causal: bool = True, scale: Optional[float] = None,
-                 workspace: Optional[torch.Tensor] = None
+                 workspace: Optional[torch.Tensor] = None, window_size: int = 0,
+                 key_mask: Optional[torch.Tensor] = None
                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """dQ, dK, dV of `attentionFwd` from dO, the forward's inputs, its output and its LSE.
 
@@ -117,6 +118,7 @@ def attentionBwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Ten
     formulation of Tyr/GPU/Kernels/MhaH100.lean:196-344.  dK and dV of a KV head are summed over
     the query heads that share it.  `workspace` may be a caller-kept float32 CUDA tensor of at
     least `backward_workspace_bytes(...) / 4` elements; one is allocated otherwise.
+    `window_size` and `key_mask` are those of the forward call (sliding window / padding keys).
     """
     _require_cuda(q, k, v, o, d_o, lse)
     B, Hq, Sq, D = q.shape
@@ -144,6 +146,16 @@ def attentionBwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Ten
                     ("dq_stride", d_q), ("dk_stride", d_k), ("dv_stride", d_v)):
         getattr(a, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
     a.dtype, a.is_causal, a.scale = _lib.TYR_ATTN_BF16, int(bool(is_causal)), float(scale or 0.0)
+    a.window_size = int(window_size)
+    if key_mask is not None:
+        if key_mask.dtype == torch.bool:
+            key_mask = key_mask.view(torch.uint8)
+        if (not key_mask.is_cuda or key_mask.dtype != torch.uint8 or key_mask.dim() != 2
+                or key_mask.stride(1) != 1 or tuple(key_mask.shape) != (B, Skv)):
+            raise ValueError("key_mask must be a uint8/bool CUDA tensor [batch, kv_seq]")
+        a.key_mask, a.key_mask_stride = key_mask.data_ptr(), key_mask.stride(0)
+    else:
+        a.key_mask, a.key_mask_stride = None, 0
     with torch.cuda.device(q.device):
         check(L.tyr_b200_attn_backward(ctypes.byref(a), _stream_ptr(q)))
     return d_q, d_k, d_v
