@@ -187,14 +187,15 @@ extern "C" lean_object* lean_launch_tyrB200AttnDecode(b_lean_obj_arg q_, b_lean_
 // Takes the place of LibTorch autograd's derivative of SDPA (`autograd.backward`,
 // Tyr/Torch.lean:742 -> cc/src/tyr.cpp:2111-2122) for callers that keep O and the LSE of
 // lean_launch_tyrB200AttnFwd.  `workspace` is a float32 CUDA tensor of at least
-// tyr_b200_attn_backward_workspace_bytes(batch, n_head, seq) bytes.
+// tyr_b200_attn_backward_workspace_bytes(batch, n_head, seq) bytes.  `window_size` is the forward's
+// (0: none); the padding-masked backward is reached through the C entry only.
 extern "C" lean_object* lean_launch_tyrB200AttnBwd(b_lean_obj_arg q_, b_lean_obj_arg k_,
                                                    b_lean_obj_arg v_, b_lean_obj_arg o_,
                                                    b_lean_obj_arg lse_, b_lean_obj_arg d_o_,
                                                    b_lean_obj_arg d_q_, b_lean_obj_arg d_k_,
                                                    b_lean_obj_arg d_v_, b_lean_obj_arg workspace_,
-                                                   uint8_t is_causal, uint64_t stream,
-                                                   lean_object* /*w*/) {
+                                                   uint8_t is_causal, uint64_t window_size,
+                                                   uint64_t stream, lean_object* /*w*/) {
   try {
     auto q = borrowTensor(q_), k = borrowTensor(k_), v = borrowTensor(v_), o = borrowTensor(o_),
          lse = borrowTensor(lse_), d_o = borrowTensor(d_o_), d_q = borrowTensor(d_q_),
@@ -228,6 +229,8 @@ extern "C" lean_object* lean_launch_tyrB200AttnBwd(b_lean_obj_arg q_, b_lean_obj
     a.dtype = TYR_ATTN_BF16;
     a.is_causal = is_causal != 0;
     a.scale = 0.f;
+    if (window_size > 0x7fffffffu) return io_error("tyrB200AttnBwd: window_size too large");
+    a.window_size = (int32_t)window_size;  // 0: none; the forward's window otherwise
     int rc = tyr_b200_attn_backward(&a, reinterpret_cast<void*>(stream));
     if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
     return lean_io_result_mk_ok(lean_box(0));

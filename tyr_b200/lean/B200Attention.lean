@@ -30,7 +30,7 @@ opaque tyrB200AttnDecode.launch
     C side: `lean_launch_tyrB200AttnBwd`. -/
 @[extern "lean_launch_tyrB200AttnBwd"]
 opaque tyrB200AttnBwd.launch
-    (q k v out lse dOut dQ dK dV workspace : @& Tensor) (isCausal : UInt8)
+    (q k v out lse dOut dQ dK dV workspace : @& Tensor) (isCausal : UInt8) (windowSize : UInt64)
     (stream : Tyr.GPU.CudaStream) : IO Unit
 
 /-- Typed wrapper: output and per-row LSE of causal / non-causal GQA attention. -/
@@ -55,7 +55,7 @@ def attentionBwd {b hq hkv s d : UInt64}
   let rows := ((s + 127) / 128) * 128
   let ws : T #[2, b, hq, rows] := torch.toFloat' (torch.zeros #[2, b, hq, rows] false (torch.device q))
   let stream ← torch.cuda_current_stream
-  tyrB200AttnBwd.launch q k v out lse dOut dQ dK dV ws (if isCausal then 1 else 0) stream
+  tyrB200AttnBwd.launch q k v out lse dOut dQ dK dV ws (if isCausal then 1 else 0) 0 stream
   pure (dQ, dK, dV)
 
 end Tyr.GPU.B200
