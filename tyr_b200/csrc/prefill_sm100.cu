@@ -72,8 +72,9 @@ struct Cfg {
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = kKOff + kKStages * kTileBytes;
-  static constexpr uint32_t kBarOff = kVOff + kVStages * kTileBytes;
-  static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2;
+  static constexpr uint32_t kOOff = kVOff + kVStages * kTileBytes;  // one O tile staged for its TMA store
+  static constexpr uint32_t kBarOff = kOOff + kTileBytes;
+  static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2 + 2;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemO = 256;
@@ -95,8 +96,10 @@ struct Bars {
   static constexpr int p_half = s_full + 2;               // [2] keys 0..63 of P_t written
   static constexpr int p_full = p_half + 2;               // [2] keys 64..127 of P_t written
   static constexpr int o_full = p_full + 2;               // [2] last PV_t of the item done
+  static constexpr int o_staged = o_full + 2;             // an O tile is in the staging buffer (4 warp arrivals)
+  static constexpr int o_stage_free = o_staged + 1;       // its TMA store has read the buffer
   __device__ static constexpr uint32_t count(int i) {
-    return (i >= p_half && i < p_half + 4) ? 4u : 1u;     // one arrival per softmax warp
+    return ((i >= p_half && i < p_half + 4) || i == o_staged) ? 4u : 1u;  // one arrival per softmax warp
   }
 };
 
@@ -242,7 +245,8 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
 template <int D, int kPoly, bool kWindow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const PrefillParams p) {
   using C = Cfg<D>;
   using B = Bars<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -251,7 +255,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
-  const uint32_t sQ = base + C::kQOff, sK = base + C::kKOff, sV = base + C::kVOff;
+  const uint32_t sQ = base + C::kQOff, sK = base + C::kKOff, sV = base + C::kVOff, sO = base + C::kOOff;
   const uint32_t sBar = base + C::kBarOff;
   auto bar = [&](int i) { return sBar + 8u * i; };
 
@@ -265,6 +269,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_o);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
@@ -407,6 +412,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
+    } else if (warp == 3) {
+      // -------------------------------------------------------- O store
+      // The softmax warps put a finished O tile into the staging buffer as bf16 (row-per-thread
+      // stores to global memory would be 32 scattered 16-byte pieces per instruction); this warp
+      // sends it out with one tiled TMA store per 64 columns and frees the buffer once the store
+      // has read it.  Use number u = 2 item + tile; the uses are strictly ordered by o_stage_free.
+      if (lane == 0) {
+        bool ok = true;
+        int u = 0;
+        for (int it = 0; ok; ++it) {
+          const int w = snake_item(it, total_items, p.snake);
+          if (w < 0) break;
+          const Item im = decode_item<kWindow>(w, p);
+#pragma unroll
+          for (int t = 0; t < 2; ++t, ++u) {
+            ok = mbar_wait(bar(B::o_staged), u & 1, abortp);
+            if (!ok) break;
+            if (im.row[t] < p.q_seq) {  // rows past the tensor are clipped by the store; a tile wholly past it is skipped
+#pragma unroll
+              for (int kb = 0; kb < C::kBoxes; ++kb)
+                tma_store_4d(&tm_o, sO + kb * C::kBoxBytes, kb * 64, im.row[t], im.hq[t], im.b);
+              tma_store_commit();
+              tma_store_wait_read0();
+            }
+            mbar_arrive(bar(B::o_stage_free));
+          }
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      }
     }
   } else {
     // ------------------------------------------------- softmax + epilogue
@@ -531,37 +565,46 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (!ok) break;
 
-      // epilogue: O_t / l -> bf16 -> global, straight from registers (each thread owns
-      // one row; its 16-byte stores fill whole 32-byte sectors pairwise)
+      // epilogue: O_t / l -> bf16 -> the staging buffer in the 128-byte-swizzled box layout of the
+      // tensor map (each thread owns one row; a warp's 16-byte pieces of 32 rows land on distinct
+      // bank groups), from where the store warp sends the tile out
       ok = mbar_wait(bar(B::o_full + t), it & 1, abortp);
+      const int use = 2 * it + t;
+      if (ok && use > 0) ok = mbar_wait(bar(B::o_stage_free), (use - 1) & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const float inv_l = 1.0f / l;
       const bool row_ok = row < p.q_seq;
-      __nv_bfloat16* orow = p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tmem_ld32(tO + c * 32, o);
         tmem_wait_ld();
         tmem_ld_ready(o);
+        const uint32_t row_base = sO + (c >> 1) * C::kBoxBytes + r * 128;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 wv;
-          wv.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv_l, __uint_as_float(o[q4 * 8 + 1]) * inv_l);
-          wv.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
-          wv.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
-          wv.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
-          if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = wv;
+          const uint32_t x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv_l, __uint_as_float(o[q4 * 8 + 1]) * inv_l);
+          const uint32_t y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
+          const uint32_t z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
+          const uint32_t wq = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
+          const int piece = (c & 1) * 4 + q4;  // 16-byte piece of the row's 128 bytes in this box
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((piece ^ (r & 7)) << 4)),
+                       "r"(x), "r"(y), "r"(z), "r"(wq)
+                       : "memory");
         }
       }
       if (p.lse != nullptr && row_ok)
         p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
-      // O_t is read: order these loads before the next item's first PV_t, which this
-      // warp gates through p_half
+      // the tile is staged: make the generic-proxy writes visible to the TMA store, then tell the
+      // store warp.  O_t is read as well: these loads are ordered before the next item's first
+      // PV_t, which this warp gates through p_half.
+      fence_proxy_async_smem();
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B::o_staged));
     }
   }
 
@@ -678,11 +721,12 @@ int sm_count() {
 template <int D, int kPoly, bool kWindow>
 int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   using C = Cfg<D>;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   int rc;
   if ((rc = make_map(&tq, a.q, a.batch, a.n_head, a.q_seq, D, a.q_stride))) return rc;
   if ((rc = make_map(&tk, a.k, a.batch, a.n_kv_head, a.kv_seq, D, a.k_stride))) return rc;
   if ((rc = make_map(&tv, a.v, a.batch, a.n_kv_head, a.kv_seq, D, a.v_stride))) return rc;
+  if ((rc = make_map(&to, a.o, a.batch, a.n_head, a.q_seq, D, a.o_stride))) return rc;
   {
     // per-device attribute, set once per device and kernel instantiation
     static std::atomic<bool> attr_set[64] = {};
@@ -738,7 +782,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   const long long items = (long long)p.items_per_group * a.n_kv_head * a.batch;
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   const int grid = (int)std::min<long long>(items, sm_count());
-  prefill_kernel<D, kPoly, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p);
+  prefill_kernel<D, kPoly, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
   count_launch();
   return (int)cudaGetLastError();
 }
