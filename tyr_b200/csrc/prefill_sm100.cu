@@ -439,7 +439,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_arrive(bar(B::o_stage_free));
           }
         }
-        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // every store has been waited for as far as its reads of shared memory go; its writes are
+        // complete when the grid is
       }
     }
   } else {
