@@ -1,7 +1,8 @@
 // Flash-attention forward for sm_100a: TMA-staged Q/K/V tiles, tcgen05.mma with
 // fp32 accumulators in tensor memory for S = Q K^T and O += P V, online softmax
 // in the exp2 domain by two softmax warpgroups that each own one 128-row Q tile,
-// P handed back to the tensor core through tensor memory, O stored from registers.
+// P handed back to the tensor core through tensor memory, O staged in shared memory and
+// written by tiled TMA stores.
 // Persistent: one CTA per SM loops over work items, longest causal rows first.
 //
 // Replaces, for bf16 CUDA tensors, the ATen call behind Tyr's typed attention
@@ -10,10 +11,12 @@
 // follows Tyr/GPU/Codegen/Macros.lean:121-163: running max, running sum, rescale
 // of the output accumulator, LSE = log(rowSum) + rowMax of the scaled scores.
 //
-// One work item = 256 query rows (two 128-row tiles) of one (batch, query head).
+// One work item = two 128-row Q tiles: 256 query rows of one (batch, query head), or the same 128
+// rows of two query heads that share a KV head.
 //   warp 0     : TMA producer (one elected lane)
 //   warp 1     : tcgen05.mma issuer (one elected lane)
 //   warp 2     : tensor-memory allocation
+//   warp 3     : TMA stores of finished O tiles out of the staging buffer (one elected lane)
 //   warps 4-7  : softmax + epilogue of Q tile 0 (thread = one row = one TMEM lane)
 //   warps 8-11 : softmax + epilogue of Q tile 1
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D);
