@@ -75,6 +75,9 @@ struct Cfg {
   static constexpr uint32_t kQOff = 0;
   static constexpr uint32_t kKOff = 2 * kTileBytes;
   static constexpr uint32_t kVOff = kKOff + kKStages * kTileBytes;
+  // O leaves through a staged tile and TMA stores where items are long (D=128); at D=64 the items of
+  // the workloads are a few tiles long and the extra hop costs more than the scattered stores do
+  static constexpr bool kStageO = (D == 128);
   static constexpr uint32_t kOOff = kVOff + kVStages * kTileBytes;  // one O tile staged for its TMA store
   static constexpr uint32_t kBarOff = kOOff + kTileBytes;
   static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2 + 2;
@@ -421,7 +424,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // stores to global memory would be 32 scattered 16-byte pieces per instruction); this warp
       // sends it out with one tiled TMA store per 64 columns and frees the buffer once the store
       // has read it.  Use number u = 2 item + tile; the uses are strictly ordered by o_stage_free.
-      if (lane == 0) {
+      if (lane == 0 && C::kStageO) {
         bool ok = true;
         int u = 0;
         for (int it = 0; ok; ++it) {
@@ -574,7 +577,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // bank groups), from where the store warp sends the tile out
       ok = mbar_wait(bar(B::o_full + t), it & 1, abortp);
       const int use = 2 * it + t;
-      if (ok && use > 0) ok = mbar_wait(bar(B::o_stage_free), (use - 1) & 1, abortp);
+      if (C::kStageO && ok && use > 0) ok = mbar_wait(bar(B::o_stage_free), (use - 1) & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -593,10 +596,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const uint32_t y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
           const uint32_t z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
           const uint32_t wq = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
-          const int piece = (c & 1) * 4 + q4;  // 16-byte piece of the row's 128 bytes in this box
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((piece ^ (r & 7)) << 4)),
-                       "r"(x), "r"(y), "r"(z), "r"(wq)
-                       : "memory");
+          if (C::kStageO) {
+            const int piece = (c & 1) * 4 + q4;  // 16-byte piece of the row's 128 bytes in this box
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((piece ^ (r & 7)) << 4)),
+                         "r"(x), "r"(y), "r"(z), "r"(wq)
+                         : "memory");
+          } else if (row_ok) {  // straight from registers: 16-byte stores of one row per thread
+            *reinterpret_cast<uint4*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s +
+                                      c * 32 + q4 * 8) = make_uint4(x, y, z, wq);
+          }
         }
       }
       if (p.lse != nullptr && row_ok)
@@ -605,10 +613,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // the tile is staged: make the generic-proxy writes visible to the TMA store, then tell the
       // store warp.  O_t is read as well: these loads are ordered before the next item's first
       // PV_t, which this warp gates through p_half.
-      fence_proxy_async_smem();
+      if (C::kStageO) fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B::o_staged));
+      if (C::kStageO && lane == 0) mbar_arrive(bar(B::o_staged));
     }
   }
 
