@@ -34,7 +34,7 @@ UNIT = "TFLOP/s"
 DEFAULT_WORKLOAD = "qwen3_0p6b_prefill"
 # dram__bytes_read.sum + dram__bytes_write.sum of one prefill launch, from the ncu
 # capture summarised in profiles/prefill_kernel_qwen3_0p6b_prefill.md (None: no capture for that workload)
-NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": 208626176}
+NCU_TRAFFIC_BYTES = {"qwen3_0p6b_prefill": 258017024}
 
 
 def load_peaks():
