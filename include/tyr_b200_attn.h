@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 5
+#define TYR_ATTN_ABI_VERSION 6
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -44,6 +44,13 @@ extern "C" {
 #define TYR_ATTN_ERR_NO_DEVICE 8   /* no sm_100 device / driver entry point missing */
 #define TYR_ATTN_ERR_DEVICE_WAIT 9 /* a bounded in-kernel wait gave up (see tyr_b200_attn_device_status) */
 #define TYR_ATTN_ERR_TOO_LARGE 10  /* size beyond a documented maximum */
+#define TYR_ATTN_ERR_RANGE 11      /* a cache position / sequence length lies outside its stated limits */
+
+/* bits of the per-device status word (tyr_b200_attn_device_status) */
+#define TYR_ATTN_STATUS_WAIT_TIMEOUT 1 /* a bounded in-kernel barrier wait ran out */
+#define TYR_ATTN_STATUS_ABORTED 2      /* a CTA left early because one of its roles gave up */
+#define TYR_ATTN_STATUS_OUT_OF_RANGE 4 /* a device-side position or length was outside its limits;
+                                          the offending rows were skipped (prologue) or clamped (decode) */
 
 /* ------------------------------------------------------------------------
  * Prefill: O = softmax(Q K^T * scale + causal) V, per-row LSE.
@@ -69,11 +76,12 @@ typedef struct TyrAttnPrefillArgs {
   int64_t o_stride[3];
   int32_t dtype;      /* TYR_ATTN_BF16 | TYR_ATTN_F32 */
   int32_t is_causal;  /* 0 | 1 */
-  float scale;        /* 0 => 1/sqrt(head_dim), ATen's default */
+  float scale;        /* <= 0 => 1/sqrt(head_dim), ATen's default */
   int32_t check_mode; /* 1 => fp32-FMA kernel (no tensor cores), any head_dim <= 256 */
   int32_t window_size; /* 0 => none; w > 0 => key j is visible to query i only if j <= i and
                           i - j < w (implies is_causal), the mask lean_torch_sdpa_gqa_window
-                          builds at cc/src/tyr.cpp:3986-3996 */
+                          builds at cc/src/tyr.cpp:3986-3996.  Needs q_seq == kv_seq, as that
+                          call has a single `seq` (cc/src/tyr.cpp:3953-3965) */
   const uint8_t* key_mask; /* NULL, or DEVICE bytes [batch, kv_seq]: 0 marks a padding key that
                               no query sees, any other value a valid key — the key/value part
                               of the padding mask of lean_torch_sdpa_gqa_mask
@@ -133,7 +141,14 @@ int tyr_b200_sdpa_gqa_mask(uint64_t batch, uint64_t n_head, uint64_t n_kv_head, 
  *          k_stride[2] and head stride kv_head_strides[b] (or, when that is
  *          NULL, len_b * k_stride[2] i.e. tightly packed).  k/v are ignored.
  * kv_lens: DEVICE int32[batch] of valid keys per sequence, or NULL for
- * max_kv_seq everywhere.  Every length must be in [1, max_kv_seq].
+ * max_kv_seq everywhere.  Every length must be in [1, max_kv_seq]; the kernels clamp
+ * a length outside that range into it (a sequence of length <= 0 gets a zero output row and
+ * LSE = -inf) and set TYR_ATTN_STATUS_OUT_OF_RANGE in the device status word.
+ * Alignment: rows are read with 16-byte copies, so every cache base pointer (dense k/v and
+ * each ragged k_ptrs[b] / v_ptrs[b]) must be 16-byte aligned and every stride, including each
+ * kv_head_strides[b], a multiple of 8 elements.  The dense form is checked by the call; the
+ * ragged arrays live on the device and are the caller's to keep aligned (the host mirror's
+ * DecodePlan checks them when it builds the arrays).
  * ---------------------------------------------------------------------- */
 typedef struct TyrAttnDecodeArgs {
   const void* q; /* [batch, n_head, head_dim] */
@@ -150,7 +165,7 @@ typedef struct TyrAttnDecodeArgs {
   int64_t o_stride[2];
   int64_t k_stride[3]; /* elements: batch, head, seq (ragged: only [2] is read) */
   int64_t v_stride[3];
-  float scale;        /* 0 => 1/sqrt(head_dim) */
+  float scale;        /* <= 0 => 1/sqrt(head_dim) */
   int32_t max_splits; /* 0 => 64; clamped to [1,64] */
   void* workspace;    /* device scratch, >= tyr_b200_attn_decode_workspace_bytes() */
   size_t workspace_bytes;
@@ -206,9 +221,19 @@ int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, 
  *   [y1, y2] -> [y1*cos - y2*sin, y1*sin + y2*cos]         (skipped when cos == NULL)
  *   out[b, h, pos_b + s, :] = bf16(y)      with pos_b = positions ? positions[b] : position0
  * cos/sin: fp32 [max_pos, head_dim/2] indexed by pos_b + s.  head_dim in {64,128,256}.
- * x, out, norm_weight, cos, sin are 16-byte aligned; strides are multiples of 8 elements.
+ * Second rotary form, Flux's (flux.applyRope, Tyr/Model/Flux/RoPE.lean:71-96): `pe` is fp32
+ * [.., max_pos, head_dim/2, 2, 2], one 2x2 matrix per position and INTERLEAVED pair:
+ *   [y_2i, y_2i+1] -> [pe[i][0][0]*y_2i + pe[i][0][1]*y_2i+1, pe[i][1][0]*y_2i + pe[i][1][1]*y_2i+1]
+ * with batch element b reading pe + b * pe_batch_stride (0 when all share one table).  cos/sin and
+ * pe exclude each other.
+ * x, out, norm_weight, cos, sin, pe are 16-byte aligned; strides are multiples of 8 elements.
  * For Q pass position0 = rotary offset and an out tensor whose row 0 is that offset
  * (out pointer already shifted); for K/V pass the cache and the sequence lengths.
+ * Limits: `cap` rows exist along the seq axis of out and `max_pos` rows in the rotary tables.
+ * With positions == NULL a call that would pass either limit is refused (-TYR_ATTN_ERR_RANGE;
+ * the reference guards its append with `cache.seq < cache.maxLen`,
+ * Tyr/Model/Qwen/Attention.lean:189).  With device-side positions the kernel skips every row
+ * whose pos_b + s falls outside a limit and sets TYR_ATTN_STATUS_OUT_OF_RANGE.
  * ---------------------------------------------------------------------- */
 typedef struct TyrAttnPrologueArgs {
   const void* x;            /* [batch, seq, n_head, head_dim] bf16 */
@@ -222,6 +247,10 @@ typedef struct TyrAttnPrologueArgs {
   int64_t x_stride[3];      /* elements: batch, seq, head */
   int64_t out_stride[3];    /* elements: batch, head, seq */
   float eps;
+  int32_t cap;              /* rows of out along seq (the cache capacity); > 0 */
+  int32_t max_pos;          /* rows of cos / sin / pe; > 0 when a rotary table is given */
+  const float* pe;          /* Flux-style [max_pos, head_dim/2, 2, 2] fp32 table or NULL */
+  int64_t pe_batch_stride;  /* elements between the tables of two batch elements (0: shared) */
 } TyrAttnPrologueArgs;
 
 int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* args, void* stream);
@@ -250,7 +279,8 @@ int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* args, void* stream);
  * `workspace` is caller-provided device memory of at least
  * tyr_b200_attn_backward_workspace_bytes() bytes (fp32 row statistics); nothing is
  * allocated by the call.  Three launches on `stream`: the row-statistics kernel, the
- * dK/dV kernel, the dQ kernel.  No sliding window or key mask in this entry point.
+ * dK/dV kernel, the dQ kernel.  `window_size` and `key_mask` select the gradients of the
+ * windowed (cc/src/tyr.cpp:3953-4018) and padding-masked (cc/src/tyr.cpp:4024-4095) calls.
  * ---------------------------------------------------------------------- */
 typedef struct TyrAttnBackwardArgs {
   const void* q;            /* [batch, n_head,    q_seq,  head_dim] */
@@ -289,9 +319,22 @@ int tyr_b200_attn_backward(const TyrAttnBackwardArgs* args, void* stream);
  * ---------------------------------------------------------------------- */
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* args, int32_t device);
 
-/* Status word the kernels' bounded waits write (0 = none gave up).  Reads the
- * word with a device synchronise; `clear` != 0 resets it. */
+/* Status word the kernels write (TYR_ATTN_STATUS_* bits; 0 = nothing to report).  Reads the
+ * word with a device synchronise; `clear` != 0 resets it.  Negative: the read itself failed. */
 int tyr_b200_attn_device_status(int32_t device, int32_t clear);
+/* The same read turned into the library's error convention, for a launcher that wants one
+ * call after its synchronise: 0, or -TYR_ATTN_ERR_DEVICE_WAIT when a bounded wait gave up,
+ * or -TYR_ATTN_ERR_RANGE when only the out-of-range bit is set.  Always clears the word. */
+int tyr_b200_attn_device_check(int32_t device);
+
+/* Test hooks for the bounded-wait path; no counterpart in the reference, not for production use.
+ * tyr_b200_attn_test_set_wait_limit: SM clock cycles any single in-kernel barrier wait may
+ * take from now on (all later launches of this process; 0 restores the default of 4e9).
+ * tyr_b200_attn_test_stalled_wait: launches a one-warp kernel whose only barrier is never
+ * arrived at, so that its wait (the same routine the attention kernels use) runs out after
+ * `limit_cycles`, sets TYR_ATTN_STATUS_WAIT_TIMEOUT and returns.  Nothing traps or faults. */
+void tyr_b200_attn_test_set_wait_limit(int64_t cycles);
+int tyr_b200_attn_test_stalled_wait(int64_t limit_cycles, void* stream);
 
 const char* tyr_b200_attn_strerror(int code);
 int tyr_b200_attn_abi_version(void);

@@ -118,3 +118,22 @@ def slice_scatter_seq(cache, start: int, src):
     out = cache.clone()
     out[:, :, start:start + src.shape[2]].copy_(src)
     return out
+
+
+def flux_rope_transpose(x, pe, weight=None, eps: float = 1e-6):
+    """QKNorm.forward (Tyr/Model/Flux/QKNorm.lean:32-39) then flux.applyRope
+    (Tyr/Model/Flux/RoPE.lean:71-96) on a projected [B,S,H,D] tensor, returned in the attention
+    layout [B,H,S,D] (the transpose_for_attention of DoubleStreamBlock.lean:179-181).
+    pe: [B, 1, S, D/2, 2, 2].  The op sequence of applyRopeAttn is kept: reshape to pairs, slice the
+    two pair elements, expand, out = pe[..., 0] * x0 + pe[..., 1] * x1."""
+    B, S, H, D = x.shape
+    if weight is not None:
+        var = (x * x).mean(-1, keepdim=True)
+        x = x * torch.rsqrt(var + eps) * weight.reshape(1, 1, 1, -1)
+    xa = x.permute(0, 2, 1, 3).contiguous().float()                    # transpose_for_attention, toFloat
+    xr = xa.reshape(B, H, S, D // 2, 1, 2)
+    x0 = xr[..., 0:1].reshape(B, H, S, D // 2, 1).expand(B, H, S, D // 2, 2)
+    x1 = xr[..., 1:2].reshape(B, H, S, D // 2, 1).expand(B, H, S, D // 2, 2)
+    pe0 = pe[..., 0:1].reshape(B, 1, S, D // 2, 2).expand(B, H, S, D // 2, 2)
+    pe1 = pe[..., 1:2].reshape(B, 1, S, D // 2, 2).expand(B, H, S, D // 2, 2)
+    return (pe0 * x0 + pe1 * x1).reshape(B, H, S, D)

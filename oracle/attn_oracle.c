@@ -365,3 +365,38 @@ void tyr_oracle_qk_prologue(const float* x, const float* weight, const float* cs
         }
       }
 }
+
+/* The same prologue with Flux's rotary form in place of the rotate-half one
+ * (flux.applyRope, Tyr/Model/Flux/RoPE.lean:71-96): the head vector is read as D/2
+ * INTERLEAVED pairs (x_2i, x_2i+1) and pair i of position `pos` is multiplied by the 2x2
+ * matrix pe[b][pos][i]: out_2i+c = pe[i][c][0]*x_2i + pe[i][c][1]*x_2i+1.  pe is
+ * [n_tables, max_pos, D/2, 2, 2]; batch element b reads table b * pe_batch_stride / (max_pos*2D),
+ * i.e. `pe + b * pe_batch_stride` (0: one shared table).  RMSNorm as above when weight != NULL
+ * (QKNorm.forward, Tyr/Model/Flux/QKNorm.lean:32-39). */
+void tyr_oracle_qk_prologue_pe(const float* x, const float* weight, const float* pe, int64_t pe_batch_stride,
+                               const int32_t* positions, int position0, float* out, int B, int S, int H,
+                               int D, int cap, float eps) {
+  for (int b = 0; b < B; ++b)
+    for (int s = 0; s < S; ++s)
+      for (int h = 0; h < H; ++h) {
+        const float* xr = x + (((int64_t)b * S + s) * H + h) * D;
+        const int pos = (positions ? positions[b] : position0) + s;
+        float* orow = out + (((int64_t)b * H + h) * cap + pos) * D;
+        const float* tab = pe + b * pe_batch_stride + (int64_t)pos * 2 * D;
+        double inv = 1.0;
+        if (weight) {
+          double ss = 0.0;
+          for (int d = 0; d < D; ++d) ss += (double)xr[d] * xr[d];
+          inv = 1.0 / sqrt(ss / D + (double)eps);
+        }
+        for (int i = 0; i < D / 2; ++i) {
+          double x0 = xr[2 * i], x1 = xr[2 * i + 1];
+          if (weight) {
+            x0 *= inv * weight[2 * i];
+            x1 *= inv * weight[2 * i + 1];
+          }
+          orow[2 * i] = (float)(tab[4 * i] * x0 + tab[4 * i + 1] * x1);
+          orow[2 * i + 1] = (float)(tab[4 * i + 2] * x0 + tab[4 * i + 3] * x1);
+        }
+      }
+}

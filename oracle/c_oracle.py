@@ -47,6 +47,8 @@ def lib() -> ctypes.CDLL:
         i32p = ctypes.POINTER(ctypes.c_int32)
         L.tyr_oracle_qk_prologue.argtypes = [f32p, f32p, f32p, f32p, i32p, ctypes.c_int, f32p] + [ctypes.c_int] * 5 + [ctypes.c_float]
         L.tyr_oracle_qk_prologue.restype = None
+        L.tyr_oracle_qk_prologue_pe.argtypes = [f32p, f32p, f32p, ctypes.c_int64, i32p, ctypes.c_int, f32p] + [ctypes.c_int] * 5 + [ctypes.c_float]
+        L.tyr_oracle_qk_prologue_pe.restype = None
         L.tyr_oracle_threads.restype = ctypes.c_int
         L.tyr_oracle_set_threads.argtypes = [ctypes.c_int]
         _lib = L
@@ -153,6 +155,23 @@ def qk_prologue(x, out, weight=None, cos=None, sin=None, positions=None, positio
     lib().tyr_oracle_qk_prologue(
         _p(x), _p(w) if w is not None else null, _p(cs) if cs is not None else null,
         _p(sn) if sn is not None else null,
+        pos.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)) if pos is not None else ctypes.POINTER(ctypes.c_int32)(),
+        int(position0), _p(out), B, S, H, D, cap, float(eps))
+    return out
+
+
+def qk_prologue_pe(x, out, pe, weight=None, positions=None, position0=0, eps=1e-6):
+    """`qk_prologue` with Flux's interleaved-pair rotary: pe [B or 1, max_pos, D/2, 2, 2] fp32."""
+    x, pe = _c(x), _c(pe)
+    assert out.dtype == np.float32 and out.flags["C_CONTIGUOUS"]
+    B, S, H, D = x.shape
+    cap = out.shape[2]
+    assert pe.shape[2:] == (D // 2, 2, 2) and pe.shape[0] in (1, B)
+    stride = 0 if pe.shape[0] == 1 else pe.shape[1] * 2 * D
+    w = _c(weight) if weight is not None else None
+    pos = np.ascontiguousarray(positions, dtype=np.int32) if positions is not None else None
+    lib().tyr_oracle_qk_prologue_pe(
+        _p(x), _p(w) if w is not None else ctypes.POINTER(ctypes.c_float)(), _p(pe), stride,
         pos.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)) if pos is not None else ctypes.POINTER(ctypes.c_int32)(),
         int(position0), _p(out), B, S, H, D, cap, float(eps))
     return out

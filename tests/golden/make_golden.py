@@ -1,6 +1,6 @@
 """Generate tests/golden/aten_sdpa.npz: outputs of the ATen operator the reference calls.
 
-Run from the repo root:  python tests/golden/make_golden.py [sdpa] [prologue] [keymask] [backward]
+Run from the repo root:  python tests/golden/make_golden.py [sdpa] [prologue] [keymask] [backward] [fluxrope]
 (no argument: all of them).
 Every case calls `oracle.aten_path` (a restatement of the `lean_torch_sdpa_*`
 forwards of cc/src/tyr.cpp around torch's scaled_dot_product_attention) on fp32
@@ -104,6 +104,24 @@ def main_prologue():
     print(path, os.path.getsize(path), "bytes")
 
 
+def main_fluxrope():
+    """tests/golden/aten_flux_rope.npz: QK-norm + Flux's interleaved rotary + transpose with torch
+    on fp32 (the chain before the joint attention of DoubleStreamBlock.lean:163-181)."""
+    g = torch.Generator(device="cpu").manual_seed(2100)
+    B, S, H, D = 2, 5, 3, 128
+    x = torch.randn(B, S, H, D, generator=g).bfloat16().float()
+    w = (torch.rand(D, generator=g) + 0.5)
+    # a rotation table per batch element and position: [[cos, -sin], [sin, cos]] per pair
+    ang = torch.rand(B, 1, S, D // 2, generator=g) * 6.0
+    pe = torch.stack([torch.stack([ang.cos(), -ang.sin()], -1), torch.stack([ang.sin(), ang.cos()], -1)], -2)
+    y = aten_path.flux_rope_transpose(x, pe, w, 1e-6)
+    out = {"x": x.numpy(), "w": w.numpy(), "pe": pe.numpy(), "y": y.numpy(),
+           "torch_version": np.array(torch.__version__)}
+    path = os.path.join(os.path.dirname(__file__), "aten_flux_rope.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes")
+
+
 # name: (B, Hq, Hkv, Sq, Skv, D, causal)
 BACKWARD_CASES = {
     "mha_causal": (1, 2, 2, 40, 40, 64, True),
@@ -135,6 +153,7 @@ def main_backward():
 
 
 if __name__ == "__main__":
-    jobs = {"sdpa": main, "prologue": main_prologue, "keymask": main_keymask, "backward": main_backward}
+    jobs = {"sdpa": main, "prologue": main_prologue, "keymask": main_keymask, "backward": main_backward,
+            "fluxrope": main_fluxrope}
     for name in (sys.argv[1:] or list(jobs)):
         jobs[name]()

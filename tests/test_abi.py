@@ -26,9 +26,9 @@ def test_library_exports_every_declared_symbol(built_lib):
 
 
 def test_abi_version_and_error_strings(built_lib):
-    assert built_lib.tyr_b200_attn_abi_version() == 5
+    assert built_lib.tyr_b200_attn_abi_version() == 6
     assert built_lib.tyr_b200_attn_strerror(0) == b"ok"
-    for code in range(1, 11):
+    for code in range(1, 12):
         assert built_lib.tyr_b200_attn_strerror(-code).startswith(b"tyr_b200_attn:")
 
 
@@ -38,6 +38,8 @@ def test_struct_sizes_match_the_c_layout():
     assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
     # 10 pointers, uint64, 6 int32, 24 int64, int32 int32 float int32, pointer, int64
     assert ctypes.sizeof(_lib.BackwardArgs) == 10 * 8 + 8 + 6 * 4 + 24 * 8 + 4 * 4 + 8 + 8
+    # 6 pointers, 5 int32 (+4 padding), 6 int64, float int32 int32 (+4 padding), pointer, int64
+    assert ctypes.sizeof(_lib.PrologueArgs) == 6 * 8 + 5 * 4 + 4 + 6 * 8 + 3 * 4 + 4 + 8 + 8
 
 
 def test_arguments_are_rejected_before_any_launch(built_lib):
@@ -61,9 +63,41 @@ def test_arguments_are_rejected_before_any_launch(built_lib):
     # dropout is refused: a Tyr build keeps its LibTorch call for it
     assert built_lib.tyr_b200_sdpa_4d(1, 1, 4, 64, p, p, p, p, 0.1, 1, None) == -6
     assert built_lib.tyr_b200_sdpa_gqa(1, 4, 2, 4, 64, p, p, p, p, 0.0, 1, 0, None) == -2  # enable_gqa off
+    # a sliding window needs one sequence length, as the reference's windowed call has
+    a.q = p
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        getattr(a, name)[:] = [4 * 8 * 64, 8 * 64, 64]
+    a.q_seq, a.kv_seq, a.window_size = 8, 4, 2
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -2
+    a.window_size = -1
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -2
     d = _lib.DecodeArgs()
     assert built_lib.tyr_b200_attn_decode(ctypes.byref(d), None) == -1
     assert built_lib.tyr_b200_attn_merge(None, None, None, None, None, None, 1, 64, None) == -1
+
+
+def test_prologue_limits_are_checked_on_the_host(built_lib):
+    a = _lib.PrologueArgs()
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -1     # NULL pointers
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    a.x = a.out = p
+    a.batch, a.seq, a.n_head, a.head_dim, a.position0 = 1, 4, 2, 64, 0
+    a.x_stride[:] = [4 * 2 * 64, 2 * 64, 64]
+    a.out_stride[:] = [2 * 8 * 64, 8 * 64, 64]
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -2     # cap not given
+    a.cap, a.position0 = 8, 5
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -11    # rows 5..8 of an 8-row cache
+    a.position0 = 2
+    a.cos = a.sin = p
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -2     # rotary table without max_pos
+    a.max_pos = 5
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -11    # positions 2..5 of a 5-row table
+    a.pe = p
+    assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -2     # two rotary forms at once
+    # the test hook refuses limits it cannot honour
+    assert built_lib.tyr_b200_attn_test_stalled_wait(0, None) == -2
 
 
 def test_backward_arguments_and_workspace(built_lib):

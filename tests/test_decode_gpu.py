@@ -103,3 +103,34 @@ def test_full_size_decode_workload():
     # idempotence: same inputs, same bits (split order is fixed)
     o2, lse2 = tnn.flashDecode(q, plan)
     assert torch.equal(o, o2) and torch.equal(lse, lse2)
+
+
+def test_lengths_outside_the_limits_are_clamped_and_reported():
+    """kv_lens above max_kv_seq would index past the grid and the workspace; the kernels clamp
+    them, a length of zero gives a defined row, and the status word says so."""
+    B, Hq, Hkv, cap, D = 3, 8, 2, 600, 128
+    kc, vc = randn(B, Hkv, cap, D, seed=11).to(DEV), randn(B, Hkv, cap, D, seed=12).to(DEV)
+    q = randn(B, Hq, D, seed=13).to(DEV)
+    tnn.device_status(0, True)
+    lens = torch.tensor([300, 100000, 0], dtype=torch.int32, device=DEV)
+    o, lse = tnn.flashDecodeDense(q, kc, vc, kv_lens=lens, kv_len=512)
+    assert tnn.device_status(0, True) & 4
+    check_seq(q[0], kc[0, :, :300], vc[0, :, :300], o[0], lse[0], "in range")
+    check_seq(q[1], kc[1, :, :512], vc[1, :, :512], o[1], lse[1], "clamped to max_kv_seq")
+    assert (o[2] == 0).all() and torch.isinf(lse[2]).all() and (lse[2] < 0).all()
+    # in-range lengths leave the status word alone
+    lens = torch.tensor([300, 512, 1], dtype=torch.int32, device=DEV)
+    tnn.flashDecodeDense(q, kc, vc, kv_lens=lens, kv_len=512)
+    assert tnn.device_status(0, True) == 0
+
+
+def test_decode_plan_rejects_misaligned_blocks():
+    base = torch.zeros(2 * 70 * 128 + 64, dtype=torch.bfloat16, device=DEV)
+    good = base[:2 * 70 * 128].view(2, 70, 128)
+    tnn.DecodePlan([good], [good], 8)
+    shifted = base[4:4 + 2 * 70 * 128].view(2, 70, 128)           # 8 bytes off a 16-byte boundary
+    with pytest.raises(ValueError):
+        tnn.DecodePlan([shifted], [shifted], 8)
+    odd_stride = torch.as_strided(base, (2, 70, 128), (70 * 128 + 4, 128, 1))   # head stride not a multiple of 8
+    with pytest.raises(ValueError):
+        tnn.DecodePlan([odd_stride], [odd_stride], 8)

@@ -268,3 +268,20 @@ def test_masked_backward_oracle_matches_autograd():
         for a, b in zip(got, want):
             np.testing.assert_allclose(a, b.numpy(), rtol=0, atol=2e-5)
         assert np.count_nonzero(got[1][0, :, 30:]) == 0 and np.count_nonzero(got[2][1, :, 5:12]) == 0
+
+
+def test_flux_rotary_prologue_matches_the_torch_chain():
+    """tyr_oracle_qk_prologue_pe against QKNorm + flux.applyRope + transpose as torch runs them
+    (tests/golden/aten_flux_rope.npz, written by tests/golden/make_golden.py fluxrope)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_flux_rope.npz"))
+    B, S, H, D = g["x"].shape
+    out = np.zeros((B, H, S, D), np.float32)
+    c_oracle.qk_prologue_pe(g["x"], out, g["pe"].reshape(B, S, D // 2, 2, 2), weight=g["w"])
+    assert np.abs(out - g["y"]).max() <= 1e-5
+    # a rotation by angle 0 is the identity (no weight: plain copy into the attention layout)
+    ident = np.zeros((1, S, D // 2, 2, 2), np.float32)
+    ident[..., 0, 0] = ident[..., 1, 1] = 1.0
+    out2 = np.zeros((B, H, S, D), np.float32)
+    c_oracle.qk_prologue_pe(g["x"], out2, ident)
+    assert np.array_equal(out2, np.transpose(g["x"], (0, 2, 1, 3)))

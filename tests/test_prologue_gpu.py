@@ -98,3 +98,76 @@ def test_rejects_bad_arguments():
     out = torch.zeros(1, 1, 4, 96, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(_lib.AttnError):
         tnn.qkPrologue(x, out)
+
+
+def test_cache_limit_rows_are_skipped_and_reported():
+    """A row that would land past the cache (the reference guards its append with
+    `cache.seq < cache.maxLen`, Tyr/Model/Qwen/Attention.lean:189) is never written: the kernel
+    skips it and raises the out-of-range bit; a guard region after the cache stays intact."""
+    from tyr_b200 import _lib
+    g = torch.Generator(device="cpu").manual_seed(17)
+    B, S, H, D, cap = 2, 4, 2, 128, 8
+    x = torch.randn(B, S, H, D, generator=g).bfloat16()
+    # one allocation: the cache of B*H*cap rows followed by a guard region of sentinels
+    store = torch.full((B * H * cap + 64, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    cache = store[:B * H * cap].view(B, H, cap, D)
+    cos, sin = rope_tables(cap, D)
+    tnn.device_status(0, True)
+    # sequence 0 fits exactly (rows 4..7); sequence 1 starts at 6: rows 8, 9 do not exist
+    pos = torch.tensor([4, 6], dtype=torch.int32)
+    ref = cache.float().cpu().numpy().copy()
+    tnn.qkPrologue(x.to(DEV), cache, None, cos.to(DEV), sin.to(DEV), positions=pos.to(DEV))
+    assert tnn.device_status(0, False) & 4
+    with pytest.raises(_lib.AttnError):
+        tnn.device_check(0)
+    assert tnn.device_status(0, True) == 0          # device_check cleared it
+    assert (store[B * H * cap:] == 7.0).all()       # guard untouched
+    c_oracle.qk_prologue(x[:1].float().numpy(), ref[:1], None, cos.numpy(), sin.numpy(), position0=4)
+    c_oracle.qk_prologue(x[1:, :2].float().numpy(), ref[1:], None, cos.numpy(), sin.numpy(), position0=6)
+    close(cache, ref)
+    # with the position known on the host the call is refused before any launch
+    with pytest.raises(ValueError):
+        tnn.qkPrologue(x.to(DEV), cache, position0=6)
+    with pytest.raises(ValueError):
+        tnn.qkPrologue(x.to(DEV), cache, None, cos[:7].contiguous().to(DEV), sin[:7].contiguous().to(DEV), position0=4)
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("shared_table", [False, True])
+def test_flux_rotary_form_against_oracle(D, shared_table):
+    g = torch.Generator(device="cpu").manual_seed(D + 1)
+    B, S, H, cap = 2, 9, 5, 16
+    x = torch.randn(B, S, H, D, generator=g).bfloat16()
+    w = torch.rand(D, generator=g) + 0.5
+    ang = torch.rand(1 if shared_table else B, cap, D // 2, generator=g) * 6.0
+    pe = torch.stack([torch.stack([ang.cos(), -ang.sin()], -1), torch.stack([ang.sin(), ang.cos()], -1)], -2).contiguous()
+    ref = np.zeros((B, H, cap, D), np.float32)
+    c_oracle.qk_prologue_pe(x.float().numpy(), ref, pe.numpy(), weight=w.numpy(), position0=3)
+    out = torch.zeros(B, H, cap, D, dtype=torch.bfloat16, device=DEV)
+    tnn.qkPrologue(x.to(DEV), out, w.to(DEV), position0=3, pe=pe.to(DEV))
+    close(out, ref)
+
+
+def test_flux_rotary_golden_chain():
+    """QKNorm + flux.applyRope + transpose as torch runs them (tests/golden/make_golden.py fluxrope)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "aten_flux_rope.npz"))
+    B, S, H, D = g["x"].shape
+    out = torch.zeros(B, H, S, D, dtype=torch.bfloat16, device=DEV)
+    pe = torch.tensor(g["pe"]).reshape(B, S, D // 2, 2, 2).contiguous()
+    tnn.qkPrologue(torch.tensor(g["x"]).bfloat16().to(DEV), out, torch.tensor(g["w"]).to(DEV), pe=pe.to(DEV))
+    close(out, g["y"])
+
+
+def test_many_heads_and_ragged_token_count():
+    # head counts that are not a multiple of the heads kept in flight, token counts that leave lane groups idle
+    g = torch.Generator(device="cpu").manual_seed(23)
+    for (B, S, H, D) in [(1, 1, 1, 128), (2, 3, 7, 64), (1, 5, 9, 256), (3, 33, 6, 128)]:
+        x = torch.randn(B, S, H, D, generator=g).bfloat16()
+        w = torch.rand(D, generator=g) + 0.5
+        cos, sin = rope_tables(S + 2, D)
+        ref = np.zeros((B, H, S + 2, D), np.float32)
+        c_oracle.qk_prologue(x.float().numpy(), ref, w.numpy(), cos.numpy(), sin.numpy(), position0=2)
+        out = torch.zeros(B, H, S + 2, D, dtype=torch.bfloat16, device=DEV)
+        tnn.qkPrologue(x.to(DEV), out, w.to(DEV), cos.to(DEV), sin.to(DEV), position0=2)
+        close(out, ref)

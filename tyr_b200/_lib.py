@@ -24,7 +24,8 @@ EXPORTS = [
     "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_decode_static",
     "tyr_b200_attn_merge", "tyr_b200_attn_qk_prologue",
     "tyr_b200_attn_backward_workspace_bytes", "tyr_b200_attn_backward",
-    "tyr_b200_attn_prefill_host", "tyr_b200_attn_device_status", "tyr_b200_attn_strerror",
+    "tyr_b200_attn_prefill_host", "tyr_b200_attn_device_status", "tyr_b200_attn_device_check",
+    "tyr_b200_attn_test_set_wait_limit", "tyr_b200_attn_test_stalled_wait", "tyr_b200_attn_strerror",
     "tyr_b200_attn_abi_version", "tyr_b200_attn_launch_count",
 ]
 
@@ -58,6 +59,7 @@ class PrologueArgs(ctypes.Structure):
         ("x", vp), ("out", vp), ("norm_weight", vp), ("cos", vp), ("sin", vp), ("positions", vp),
         ("position0", c_i32), ("batch", c_i32), ("seq", c_i32), ("n_head", c_i32), ("head_dim", c_i32),
         ("x_stride", c_i64 * 3), ("out_stride", c_i64 * 3), ("eps", c_f32),
+        ("cap", c_i32), ("max_pos", c_i32), ("pe", vp), ("pe_batch_stride", c_i64),
     ]
 
 
@@ -118,6 +120,12 @@ def load() -> ctypes.CDLL:
     L.tyr_b200_attn_merge.restype = ctypes.c_int
     L.tyr_b200_attn_device_status.argtypes = [c_i32, c_i32]
     L.tyr_b200_attn_device_status.restype = ctypes.c_int
+    L.tyr_b200_attn_device_check.argtypes = [c_i32]
+    L.tyr_b200_attn_device_check.restype = ctypes.c_int
+    L.tyr_b200_attn_test_set_wait_limit.argtypes = [c_i64]
+    L.tyr_b200_attn_test_set_wait_limit.restype = None
+    L.tyr_b200_attn_test_stalled_wait.argtypes = [c_i64, vp]
+    L.tyr_b200_attn_test_stalled_wait.restype = ctypes.c_int
     L.tyr_b200_attn_strerror.argtypes = [ctypes.c_int]
     L.tyr_b200_attn_strerror.restype = ctypes.c_char_p
     L.tyr_b200_attn_abi_version.restype = ctypes.c_int

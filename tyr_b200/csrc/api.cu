@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "attn_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace tyr {
 namespace {
@@ -34,7 +35,11 @@ HostStage g_stage[kMaxDevices];
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-float resolve_scale(float scale, int d) { return scale != 0.f ? scale : 1.0f / std::sqrt((float)d); }
+// scale <= 0 (or NaN) selects ATen's default 1/sqrt(head_dim); the kernels take the row maximum
+// of the raw scores before scaling, which is only valid for a positive scale
+float resolve_scale(float scale, int d) { return scale > 0.f ? scale : 1.0f / std::sqrt((float)d); }
+
+std::atomic<long long> g_wait_limit{0};  // 0: the compiled default
 
 int current_device_checked(int* dev) {
   cudaError_t e = cudaGetDevice(dev);
@@ -52,7 +57,9 @@ int check_prefill(const TyrAttnPrefillArgs* a) {
   if (a->dtype != TYR_ATTN_BF16 && a->dtype != TYR_ATTN_F32) return -TYR_ATTN_ERR_DTYPE;
   if (a->dtype == TYR_ATTN_F32 && !a->check_mode) return -TYR_ATTN_ERR_DTYPE;
   if (a->n_head > 65535 || a->batch > 65535) return -TYR_ATTN_ERR_TOO_LARGE;
-  if (a->window_size < 0) return -TYR_ATTN_ERR_SHAPE;
+  // the windowed call has one sequence length (cc/src/tyr.cpp:3953-3965); with more queries than
+  // keys + window an item would have no key tile at all
+  if (a->window_size < 0 || (a->window_size > 0 && a->q_seq != a->kv_seq)) return -TYR_ATTN_ERR_SHAPE;
   if (a->key_mask && a->batch > 1 && a->key_mask_stride < a->kv_seq) return -TYR_ATTN_ERR_SHAPE;
   if (!a->check_mode) {
     if (a->head_dim != 64 && a->head_dim != 128) return -TYR_ATTN_ERR_HEAD_DIM;
@@ -123,6 +130,11 @@ DeviceState* device_state(int device) {
 }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+long long wait_limit_cycles() {
+  const long long v = g_wait_limit.load(std::memory_order_relaxed);
+  return v > 0 ? v : 4000000000ll;
+}
 
 }  // namespace tyr
 
@@ -226,14 +238,27 @@ int tyr_b200_attn_merge(const float* o_a, const float* lse_a, const float* o_b, 
 int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* a, void* stream) {
   if (!a || !a->x || !a->out) return -TYR_ATTN_ERR_NULL;
   if ((a->cos == nullptr) != (a->sin == nullptr)) return -TYR_ATTN_ERR_NULL;
+  if (a->pe && a->cos) return -TYR_ATTN_ERR_SHAPE;  // one rotary form per call
   if (a->batch <= 0 || a->seq <= 0 || a->n_head <= 0 || a->position0 < 0) return -TYR_ATTN_ERR_SHAPE;
   if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return -TYR_ATTN_ERR_HEAD_DIM;
+  // every written row and every rotary row must exist: the reference guards its append with
+  // `cache.seq < cache.maxLen` (Tyr/Model/Qwen/Attention.lean:189)
+  if (a->cap <= 0 || ((a->cos || a->pe) && a->max_pos <= 0)) return -TYR_ATTN_ERR_SHAPE;
+  if (!a->positions) {
+    if ((int64_t)a->position0 + a->seq > a->cap) return -TYR_ATTN_ERR_RANGE;
+    if ((a->cos || a->pe) && (int64_t)a->position0 + a->seq > a->max_pos) return -TYR_ATTN_ERR_RANGE;
+  }
   if (!aligned16(a->x) || !aligned16(a->out) || (a->norm_weight && !aligned16(a->norm_weight)) ||
-      (a->cos && (!aligned16(a->cos) || !aligned16(a->sin))))
+      (a->cos && (!aligned16(a->cos) || !aligned16(a->sin))) || (a->pe && !aligned16(a->pe)))
     return -TYR_ATTN_ERR_ALIGN;
   for (int i = 0; i < 3; ++i)
     if ((a->x_stride[i] & 7) || (a->out_stride[i] & 7)) return -TYR_ATTN_ERR_ALIGN;
-  return launch_qk_prologue(*a, static_cast<cudaStream_t>(stream));
+  if (a->pe && (a->pe_batch_stride & 3)) return -TYR_ATTN_ERR_ALIGN;
+  int dev = 0, rc;
+  if ((rc = current_device_checked(&dev))) return rc;
+  DeviceState* ds = device_state(dev);
+  if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+  return launch_qk_prologue(*a, ds->status, static_cast<cudaStream_t>(stream));
 }
 
 uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, int32_t q_seq) {
@@ -314,39 +339,58 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   if (!hs.out_stream &&
       (e = cudaStreamCreateWithFlags(&hs.out_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail((int)e);
-  // Pipeline over the batch: while chunk i computes and chunk i-1 drains to the host on
-  // the device->host copy engine, chunk i+1 is already arriving on the host->device one.
-  const int n_chunks = a->batch < kMaxHostChunks ? a->batch : kMaxHostChunks;
+  // Pipeline over (batch, KV-head range) chunks: while chunk i computes and chunk i-1 drains to
+  // the host on the device->host copy engine, chunk i+1 is already arriving on the
+  // host->device one.  In [batch, heads, seq, dim] storage the heads of one batch element are
+  // contiguous, so a chunk is one contiguous piece of each tensor; the more chunks, the less of
+  // each copy direction is left uncovered at the two ends of the pipeline.
+  const int g = a->n_head / a->n_kv_head;
+  const int per_batch = a->batch >= kMaxHostChunks ? 1 : std::min<int>(a->n_kv_head, kMaxHostChunks / a->batch);
+  const int batch_chunks = a->batch >= kMaxHostChunks ? kMaxHostChunks : a->batch;
   cudaStream_t st = hs.stream, so = hs.out_stream;
   const char *hq = static_cast<const char*>(a->q), *hk = static_cast<const char*>(a->k),
              *hv = static_cast<const char*>(a->v);
   char* ho = static_cast<char*>(a->o);
-  const size_t q1 = nq / a->batch * es, k1 = nk / a->batch * es, l1 = nl / a->batch * 4;
-  for (int c = 0; c < n_chunks; ++c) {
-    const int b0 = (int)((long long)a->batch * c / n_chunks), b1 = (int)((long long)a->batch * (c + 1) / n_chunks);
-    const size_t nb = (size_t)(b1 - b0);
-    if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
-      return fail((int)e);
-    if ((e = cudaMemcpyAsync(base + b0 * q1, hq + b0 * q1, nb * q1, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-        (e = cudaMemcpyAsync(base + off_k + b0 * k1, hk + b0 * k1, nb * k1, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-        (e = cudaMemcpyAsync(base + off_v + b0 * k1, hv + b0 * k1, nb * k1, cudaMemcpyHostToDevice, st)) != cudaSuccess)
-      return fail((int)e);
-    TyrAttnPrefillArgs dc = d;
-    dc.batch = (int32_t)nb;
-    dc.q = base + b0 * q1;
-    dc.k = base + off_k + b0 * k1;
-    dc.v = base + off_v + b0 * k1;
-    dc.o = base + off_o + b0 * q1;
-    dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + b0 * l1) : nullptr;
-    rc = tyr_b200_attn_prefill(&dc, st);
-    if (rc) return fail(rc);
-    if ((e = cudaEventRecord(hs.done[c], st)) != cudaSuccess ||
-        (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
-        (e = cudaMemcpyAsync(ho + b0 * q1, base + off_o + b0 * q1, nb * q1, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
-      return fail((int)e);
-    if (a->lse && (e = cudaMemcpyAsync(reinterpret_cast<char*>(a->lse) + b0 * l1, base + off_l + b0 * l1,
-                                       nb * l1, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
-      return fail((int)e);
+  const size_t qh1 = (size_t)a->q_seq * a->head_dim * es;   // one query head of one batch element
+  const size_t kh1 = (size_t)a->kv_seq * a->head_dim * es;  // one KV head
+  const size_t lh1 = (size_t)a->q_seq * 4;
+  int c = 0;
+  for (int bc = 0; bc < batch_chunks; ++bc) {
+    const int b0 = (int)((long long)a->batch * bc / batch_chunks), b1 = (int)((long long)a->batch * (bc + 1) / batch_chunks);
+    for (int hc = 0; hc < per_batch; ++hc, ++c) {
+      const int h0 = (int)((long long)a->n_kv_head * hc / per_batch), h1 = (int)((long long)a->n_kv_head * (hc + 1) / per_batch);
+      // per_batch > 1 only with one batch element per chunk, so the piece stays contiguous
+      const size_t nbat = (size_t)(b1 - b0), nkv = (size_t)(h1 - h0);
+      const size_t q_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * qh1, q_len = (per_batch > 1 ? nkv * g : nbat * a->n_head) * qh1;
+      const size_t k_off = ((size_t)b0 * a->n_kv_head + h0) * kh1, k_len = (per_batch > 1 ? nkv : nbat * a->n_kv_head) * kh1;
+      const size_t l_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * lh1, l_len = (per_batch > 1 ? nkv * g : nbat * a->n_head) * lh1;
+      if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
+        return fail((int)e);
+      if ((e = cudaMemcpyAsync(base + q_off, hq + q_off, q_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+          (e = cudaMemcpyAsync(base + off_k + k_off, hk + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+          (e = cudaMemcpyAsync(base + off_v + k_off, hv + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        return fail((int)e);
+      TyrAttnPrefillArgs dc = d;
+      dc.batch = (int32_t)nbat;
+      if (per_batch > 1) {
+        dc.n_kv_head = (int32_t)nkv;
+        dc.n_head = (int32_t)(nkv * g);
+      }
+      dc.q = base + q_off;
+      dc.k = base + off_k + k_off;
+      dc.v = base + off_v + k_off;
+      dc.o = base + off_o + q_off;
+      dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + l_off) : nullptr;
+      rc = tyr_b200_attn_prefill(&dc, st);
+      if (rc) return fail(rc);
+      if ((e = cudaEventRecord(hs.done[c], st)) != cudaSuccess ||
+          (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
+          (e = cudaMemcpyAsync(ho + q_off, base + off_o + q_off, q_len, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+        return fail((int)e);
+      if (a->lse && (e = cudaMemcpyAsync(reinterpret_cast<char*>(a->lse) + l_off, base + off_l + l_off, l_len,
+                                         cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+        return fail((int)e);
+    }
   }
   e = cudaStreamSynchronize(so);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
@@ -367,6 +411,26 @@ int tyr_b200_attn_device_status(int32_t device, int32_t clear) {
   return v;
 }
 
+int tyr_b200_attn_device_check(int32_t device) {
+  const int v = tyr_b200_attn_device_status(device, 1);
+  if (v <= 0) return v;
+  if (v & (kStatusWaitTimeout | kStatusAborted)) return -TYR_ATTN_ERR_DEVICE_WAIT;
+  return -TYR_ATTN_ERR_RANGE;
+}
+
+void tyr_b200_attn_test_set_wait_limit(int64_t cycles) {
+  g_wait_limit.store(cycles > 0 ? (long long)cycles : 0, std::memory_order_relaxed);
+}
+
+int tyr_b200_attn_test_stalled_wait(int64_t limit_cycles, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 4000000000ll) return -TYR_ATTN_ERR_SHAPE;
+  int dev = 0, rc;
+  if ((rc = current_device_checked(&dev))) return rc;
+  DeviceState* ds = device_state(dev);
+  if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+  return launch_stalled_wait((long long)limit_cycles, ds->status, static_cast<cudaStream_t>(stream));
+}
+
 const char* tyr_b200_attn_strerror(int code) {
   if (code == 0) return "ok";
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -381,6 +445,7 @@ const char* tyr_b200_attn_strerror(int code) {
     case TYR_ATTN_ERR_NO_DEVICE: return "tyr_b200_attn: no usable CUDA device or driver entry point";
     case TYR_ATTN_ERR_DEVICE_WAIT: return "tyr_b200_attn: a bounded in-kernel wait gave up";
     case TYR_ATTN_ERR_TOO_LARGE: return "tyr_b200_attn: size beyond the supported maximum";
+    case TYR_ATTN_ERR_RANGE: return "tyr_b200_attn: a cache position or sequence length lies outside its limits";
     default: return "tyr_b200_attn: unknown error";
   }
 }

@@ -15,6 +15,12 @@ struct DeviceState {
 };
 DeviceState* device_state(int device);  // lazily created; nullptr on failure
 void count_launch(int n = 1);
+// Cycles a single in-kernel barrier wait may take before its CTA gives up (api.cu; the default
+// unless a test shortened it).
+long long wait_limit_cycles();
+// ptx_sm100.cuh users only: a one-warp kernel whose only barrier is never arrived at, so that its
+// bounded wait runs out after `limit_cycles` (stalled_wait.cu).
+int launch_stalled_wait(long long limit_cycles, int* status, cudaStream_t st);
 
 // prefill_sm100.cu — tcgen05/TMA kernel, bf16, head_dim in {64,128}.
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st);
@@ -34,6 +40,6 @@ int launch_merge2(const float* o_a, const float* lse_a, const float* o_b, const 
                   float* o_out, float* lse_out, int64_t rows, int head_dim, cudaStream_t st);
 
 // qk_prologue.cu
-int launch_qk_prologue(const TyrAttnPrologueArgs& a, cudaStream_t st);
+int launch_qk_prologue(const TyrAttnPrologueArgs& a, int* status, cudaStream_t st);
 
 }  // namespace tyr

@@ -90,6 +90,7 @@ struct BwdParams {
   int n_qblk, n_kblk;
   float sl2, scale;
   int* status;
+  long long wait_limit;  // cycles any single barrier wait may take before the CTA gives up
 };
 
 constexpr uint32_t kBwdDescHi = umma_desc_hi(1024);
@@ -174,7 +175,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   using C = BCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ WaitCtl wait_ctl;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
@@ -184,7 +185,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   const int n_units = p.n_kblk * p.n_kv_head * p.batch;
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
+    wait_ctl.abort = 0;
+    wait_ctl.limit = p.wait_limit;
     for (int i = 0; i < C::kNumBars; ++i)
       mbar_init(bar(i), (i == C::p_full || i == C::p_half || i == C::acc_free) ? 8u
                         : (i >= C::pair && i < C::pair + 4) ? 2u : 1u);
@@ -202,7 +204,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  volatile int* abortp = &abort_flag;
+  volatile WaitCtl* abortp = &wait_ctl;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -451,14 +453,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (abort_flag != 0) {
+  if (wait_ctl.abort != 0) {
     // Some wait gave up.  Give this CTA's outstanding TMA loads a bounded time
     // to land before the shared memory goes away, then report.
     if (threadIdx.x == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
-      atomicOr(p.status, abort_flag);
+      atomicOr(p.status, wait_ctl.abort);
     }
     __syncthreads();
   }
@@ -532,7 +534,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   using C = DqCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ WaitCtl wait_ctl;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -542,7 +544,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int n_units = p.n_qblk * p.n_head * p.batch;
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
+    wait_ctl.abort = 0;
+    wait_ctl.limit = p.wait_limit;
     for (int i = 0; i < C::kNumBars; ++i)
       mbar_init(bar(i), (i == C::sdp_free || i == C::p_full || i == C::p_full + 1 || i == C::acc_free) ? 8u : 1u);
     mbar_fence_init();
@@ -559,7 +562,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  volatile int* abortp = &abort_flag;
+  volatile WaitCtl* abortp = &wait_ctl;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -771,12 +774,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (abort_flag != 0) {
+  if (wait_ctl.abort != 0) {
     if (threadIdx.x == 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) {
       }
-      atomicOr(p.status, abort_flag);
+      atomicOr(p.status, wait_ctl.abort);
     }
     __syncthreads();
   }
@@ -886,6 +889,7 @@ int launch_bwd(const TyrAttnBackwardArgs& a, float scale, int* status, cudaStrea
   p.scale = scale;
   p.sl2 = scale * kLog2e;
   p.status = status;
+  p.wait_limit = wait_limit_cycles();
 
   int sms = 148;
   {

@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "attn_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace tyr {
 namespace {
@@ -44,7 +45,18 @@ struct DecodeParams {
   int chunk_len, n_splits;
   float* ws_o;    // [batch, n_head, n_splits, D] normalised partial outputs
   float* ws_lse;  // [batch, n_head, n_splits] log2-domain partial LSE
+  int* status;    // per-device status word (out-of-range lengths are reported there)
 };
+
+// Length of sequence b, forced into [0, max_kv_seq]: the workspace and the grid are sized for
+// max_kv_seq, so a longer length would index past both.
+__device__ __forceinline__ int clamped_len(const DecodeParams& p, int b, bool report) {
+  if (!p.kv_lens) return p.max_kv_seq;
+  const int raw = p.kv_lens[b];
+  const int len = min(max(raw, 0), p.max_kv_seq);
+  if (report && (len != raw || raw == 0)) atomicOr(p.status, kStatusOutOfRange);
+  return len;
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -111,8 +123,17 @@ decode_kernel(const DecodeParams p) {
   const int hkv = blockIdx.y / p.head_groups;
   const int hg = blockIdx.y % p.head_groups;
   const int b = blockIdx.z;
-  const int len = p.kv_lens ? p.kv_lens[b] : p.max_kv_seq;
+  const int len = clamped_len(p, b, split == 0 && threadIdx.x == 0 && blockIdx.y == 0);
   const int n_chunks = (len + p.chunk_len - 1) / p.chunk_len;
+  if (len == 0 && split == 0) {
+    // no key at all: a defined row (zeros, LSE = -inf) instead of stale memory
+    const int head0 = hkv * p.group + hg * 16, heads_here = min(16, p.group - hg * 16);
+    for (int idx = threadIdx.x; idx < heads_here * D; idx += kThreads) {
+      const int head = head0 + idx / D, d = idx % D;
+      p.o[b * p.os[0] + (int64_t)head * p.os[1] + d] = __float2bfloat16_rn(0.f);
+      if (d == 0 && p.lse) p.lse[(int64_t)b * p.n_head + head] = -INFINITY;
+    }
+  }
   if (split >= n_chunks) return;
   const int key_begin = split * p.chunk_len;
   const int key_end = min(len, key_begin + p.chunk_len);
@@ -317,7 +338,7 @@ template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const DecodeParams p) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int len = p.kv_lens ? p.kv_lens[b] : p.max_kv_seq;
+  const int len = clamped_len(p, b, false);
   const int n_chunks = (len + p.chunk_len - 1) / p.chunk_len;
   if (n_chunks <= 1) return;  // the split kernel already wrote the final row
   const int64_t slot0 = ((int64_t)b * p.n_head + head) * p.n_splits;
@@ -405,6 +426,13 @@ int launch_decode(const TyrAttnDecodeArgs& a, float scale, cudaStream_t st) {
   p.n_splits = decode_num_splits(a.max_kv_seq, a.max_splits, &p.chunk_len);
   p.ws_o = nullptr;
   p.ws_lse = nullptr;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -TYR_ATTN_ERR_NO_DEVICE;
+    DeviceState* ds = device_state(dev);
+    if (!ds) return -TYR_ATTN_ERR_NO_DEVICE;
+    p.status = ds->status;
+  }
   if (p.n_splits > 1) {
     const size_t need = decode_workspace_bytes(a.batch, a.n_head, a.head_dim, a.max_kv_seq, a.max_splits);
     if (a.workspace == nullptr || a.workspace_bytes < need) return -TYR_ATTN_ERR_WORKSPACE;

@@ -13,6 +13,7 @@ namespace tyr {
 enum : int {
   kStatusWaitTimeout = 1,   // an mbarrier wait gave up
   kStatusAborted = 2,       // a CTA left early because another role gave up
+  kStatusOutOfRange = 4,    // a device-side index (cache position, sequence length) was outside its limits
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -55,25 +56,33 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-// Wait limit for any single mbarrier phase, in SM clock cycles (2-4 s at 1-2 GHz).  Far
+// Default wait limit for any single mbarrier phase, in SM clock cycles (2-4 s at 1-2 GHz).  Far
 // above any legitimate wait (the longest is one KV tile of work, microseconds) and
 // short enough that a protocol error ends the kernel instead of holding the GPU.
 constexpr long long kWaitLimitCycles = 4000000000ll;
 
-// Bounded wait.  `abort_flag` is a CTA-shared word: non-zero means some role of
-// this CTA already gave up, so everyone else leaves too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// CTA-shared control block of the bounded waits: `abort` non-zero means some role of this CTA
+// already gave up, so everyone else leaves too; `limit` is the wait limit in cycles, copied
+// from the kernel parameters by the thread that initialises the barriers.
+struct WaitCtl {
+  int abort;
+  int pad;
+  long long limit;
+};
+
+// Bounded wait.  The limit is only looked at on the slow path, after a first poll has failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitCtl* ctl) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
 #pragma unroll 1
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
+    if (ctl->abort) return false;
     const long long now = clock64();
     if (t0 == 0) {
       t0 = now;
-    } else if (now - t0 > kWaitLimitCycles) {
-      *abort_flag = kStatusWaitTimeout;
+    } else if (now - t0 > ctl->limit) {
+      ctl->abort = kStatusWaitTimeout;
       return false;
     }
   }
@@ -96,7 +105,6 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
-// 4-D tiled store, shared -> global (rows outside the tensor are clipped).
 // Untiled bulk copy global -> shared, completion counted in bytes on `bar`.  Both addresses
 // 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -105,6 +113,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// 4-D tiled store, shared -> global (rows outside the tensor are clipped).
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1,
                                              int c2, int c3) {
   asm volatile(
@@ -358,33 +367,6 @@ __device__ __forceinline__ float max3_f32(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-
-// 2^t for two values on the FMA pipe instead of the special-function unit:
-// n = round(t) taken from the mantissa of t + 1.5*2^23, f = t - n in [-0.5, 0.5],
-// cubic through the Chebyshev nodes of that interval (relative error 1.0e-4, below
-// the 3.9e-3 step of the bf16 value it is rounded to), then n added to the exponent.
-// t is clamped at -125 so the exponent never wraps; -inf gives 2^-125.
-__device__ __forceinline__ void ex2_poly_x2(uint64_t t2, float& p0, float& p1) {
-  float t0, t1;
-  unpack_f32x2(t2, t0, t1);
-  t0 = fmaxf(t0, -125.0f);
-  t1 = fmaxf(t1, -125.0f);
-  const uint64_t tc = pack_f32x2(t0, t1);
-  const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);
-  const uint64_t nmagic = pack_f32x2(-12582912.0f, -12582912.0f);
-  const uint64_t r = add_f32x2(tc, magic);                  // low mantissa bits = round(t)
-  const uint64_t n = add_f32x2(r, nmagic);
-  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.0f, -1.0f), tc);
-  uint64_t p = fma_f32x2(pack_f32x2(0.05583828315f, 0.05583828315f), f,
-                         pack_f32x2(0.2426394820f, 0.2426394820f));
-  p = fma_f32x2(p, f, pack_f32x2(0.6931367517f, 0.6931367517f));
-  p = fma_f32x2(p, f, pack_f32x2(0.9999245405f, 0.9999245405f));
-  uint32_t pb0, pb1, rb0, rb1;
-  unpack_u32x2(p, pb0, pb1);
-  unpack_u32x2(r, rb0, rb1);
-  p0 = __uint_as_float(pb0 + (rb0 << 23));
-  p1 = __uint_as_float(pb1 + (rb1 << 23));
 }
 
 }  // namespace tyr

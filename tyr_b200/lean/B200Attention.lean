@@ -30,8 +30,29 @@ opaque tyrB200AttnDecode.launch
     C side: `lean_launch_tyrB200AttnBwd`. -/
 @[extern "lean_launch_tyrB200AttnBwd"]
 opaque tyrB200AttnBwd.launch
-    (q k v out lse dOut dQ dK dV workspace : @& Tensor) (isCausal : UInt8) (windowSize : UInt64)
+    (q k v out lse dOut dQ dK dV workspace keyMask : @& Tensor) (isCausal : UInt8) (windowSize : UInt64)
     (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- Single-token decode with one cached length per sequence (`kvLens : int32 [batch]`, the
+    per-sequence form of `KVCache.seq`).  C side: `lean_launch_tyrB200AttnDecodeRagged`. -/
+@[extern "lean_launch_tyrB200AttnDecodeRagged"]
+opaque tyrB200AttnDecodeRagged.launch
+    (q kCache vCache kvLens out workspace : @& Tensor) (maxKvLen : UInt64)
+    (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- Fused head norm + rotary + layout change + in-place cache append for one projected tensor
+    (`x : [batch, seq, heads, headDim]` into `out : [batch, heads, cap, headDim]` at rows
+    `positions[b] + s`).  Tensors with no elements skip a step.  C side: `lean_launch_tyrB200QkPrologue`. -/
+@[extern "lean_launch_tyrB200QkPrologue"]
+opaque tyrB200QkPrologue.launch
+    (x out normWeight cos sin positions : @& Tensor) (position0 : UInt64) (eps : Float)
+    (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- LSE merge of two partial attention results over disjoint key sets (`ringAttnReduce`).
+    C side: `lean_launch_tyrB200AttnMerge`. -/
+@[extern "lean_launch_tyrB200AttnMerge"]
+opaque tyrB200AttnMerge.launch
+    (oA lseA oB lseB oOut lseOut : @& Tensor) (stream : Tyr.GPU.CudaStream) : IO Unit
 
 /-- Typed wrapper: output and per-row LSE of causal / non-causal GQA attention. -/
 def attentionFwd {b hq hkv s d : UInt64}
@@ -55,7 +76,8 @@ def attentionBwd {b hq hkv s d : UInt64}
   let rows := ((s + 127) / 128) * 128
   let ws : T #[2, b, hq, rows] := torch.toFloat' (torch.zeros #[2, b, hq, rows] false (torch.device q))
   let stream ← torch.cuda_current_stream
-  tyrB200AttnBwd.launch q k v out lse dOut dQ dK dV ws (if isCausal then 1 else 0) 0 stream
+  let noMask : T #[0] := torch.zeros #[0] false (torch.device q)
+  tyrB200AttnBwd.launch q k v out lse dOut dQ dK dV ws noMask (if isCausal then 1 else 0) 0 stream
   pure (dQ, dK, dV)
 
 end Tyr.GPU.B200

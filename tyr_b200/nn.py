@@ -255,6 +255,11 @@ class DecodePlan:
                 raise ValueError("K and V of a sequence must match in shape, stride and be bf16")
             if kt.stride(1) != self.head_dim:
                 raise ValueError("keys of one head must be contiguous rows")
+            # the kernel reads rows with 16-byte copies straight from these pointers
+            if kt.data_ptr() % 16 or vt.data_ptr() % 16 or kt.stride(0) % 8:
+                raise ValueError("each K/V block must be 16-byte aligned with a head stride that is a multiple of 8")
+            if kt.shape[1] < 1:
+                raise ValueError("every sequence needs at least one cached key")
             lens.append(kt.shape[1]); kp.append(kt.data_ptr()); vp.append(vt.data_ptr()); hs.append(kt.stride(0))
         self._keep = (list(k_list), list(v_list))
         self.max_kv_seq = max(lens)
@@ -268,6 +273,23 @@ class DecodePlan:
                                                                   self.max_kv_seq, max_splits)
         self.workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
         self.workspace_bytes = nbytes
+
+
+def _fill_decode(q3, plan: DecodePlan, out, lse, scale) -> DecodeArgs:
+    """Arguments of a ragged decode call over `plan`, without the workspace."""
+    a = DecodeArgs()
+    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), (lse.data_ptr() if lse is not None else None)
+    a.k = a.v = None
+    a.k_ptrs, a.v_ptrs = plan.k_ptrs.data_ptr(), plan.v_ptrs.data_ptr()
+    a.kv_lens, a.kv_head_strides = plan.kv_lens.data_ptr(), plan.head_strides.data_ptr()
+    a.batch, a.n_head, a.n_kv_head = plan.batch, plan.n_head, plan.n_kv_head
+    a.max_kv_seq, a.head_dim = plan.max_kv_seq, plan.head_dim
+    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
+    a.o_stride[:] = [out.stride(0), out.stride(1)]
+    a.k_stride[:] = [0, 0, plan.head_dim]
+    a.v_stride[:] = [0, 0, plan.head_dim]
+    a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    return a
 
 
 def flashDecode(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] = None,
@@ -288,18 +310,7 @@ def flashDecode(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] = None
         out = torch.empty((plan.batch, plan.n_head, plan.head_dim), dtype=q.dtype, device=q.device)
     if lse is None and return_lse:
         lse = torch.empty((plan.batch, plan.n_head), dtype=torch.float32, device=q.device)
-    a = DecodeArgs()
-    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), (lse.data_ptr() if lse is not None else None)
-    a.k = a.v = None
-    a.k_ptrs, a.v_ptrs = plan.k_ptrs.data_ptr(), plan.v_ptrs.data_ptr()
-    a.kv_lens, a.kv_head_strides = plan.kv_lens.data_ptr(), plan.head_strides.data_ptr()
-    a.batch, a.n_head, a.n_kv_head = plan.batch, plan.n_head, plan.n_kv_head
-    a.max_kv_seq, a.head_dim = plan.max_kv_seq, plan.head_dim
-    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
-    a.o_stride[:] = [out.stride(0), out.stride(1)]
-    a.k_stride[:] = [0, 0, plan.head_dim]
-    a.v_stride[:] = [0, 0, plan.head_dim]
-    a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    a = _fill_decode(q3, plan, out, lse, scale)
     a.workspace, a.workspace_bytes = plan.workspace.data_ptr(), plan.workspace_bytes
     with torch.cuda.device(q.device):
         check(_lib.load().tyr_b200_attn_decode(ctypes.byref(a), _stream_ptr(q)))
@@ -331,18 +342,7 @@ def flashDecodeStatic(q: torch.Tensor, plan: DecodePlan, scale: Optional[float] 
         out = torch.empty((plan.batch, plan.n_head, plan.head_dim), dtype=q.dtype, device=q.device)
     if lse is None:
         lse = torch.empty((plan.batch, plan.n_head), dtype=torch.float32, device=q.device)
-    a = DecodeArgs()
-    a.q, a.o, a.lse = q3.data_ptr(), out.data_ptr(), lse.data_ptr()
-    a.k = a.v = None
-    a.k_ptrs, a.v_ptrs = plan.k_ptrs.data_ptr(), plan.v_ptrs.data_ptr()
-    a.kv_lens, a.kv_head_strides = plan.kv_lens.data_ptr(), plan.head_strides.data_ptr()
-    a.batch, a.n_head, a.n_kv_head = plan.batch, plan.n_head, plan.n_kv_head
-    a.max_kv_seq, a.head_dim = plan.max_kv_seq, plan.head_dim
-    a.q_stride[:] = [q3.stride(0), q3.stride(1)]
-    a.o_stride[:] = [out.stride(0), out.stride(1)]
-    a.k_stride[:] = [0, 0, plan.head_dim]
-    a.v_stride[:] = [0, 0, plan.head_dim]
-    a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    a = _fill_decode(q3, plan, out, lse, scale)
     a.workspace, a.workspace_bytes = None, 0      # ignored: the library's own array is used
     with torch.cuda.device(q.device):
         check(_lib.load().tyr_b200_attn_decode_static(ctypes.byref(a), _stream_ptr(q)))
@@ -385,7 +385,8 @@ def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
                cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
-               positions: Optional[torch.Tensor] = None, position0: int = 0, eps: float = 1e-6):
+               positions: Optional[torch.Tensor] = None, position0: int = 0, eps: float = 1e-6,
+               pe: Optional[torch.Tensor] = None):
     """Fused per-head RMSNorm + rotary embedding + [B,S,H,D] -> [B,H,S,D] layout change,
     written into `out` [B,H,cap,D] at rows positions[b] + s (in place: a KV-cache append
     when `out` is the cache).  One pass instead of applyHeadNorm
@@ -393,6 +394,12 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     transpose_for_attention (Tyr/Torch.lean:589-597) and data.sliceScatter
     (Tyr/Model/Qwen/Attention.lean:189-193).  `norm_weight` [D] and `cos`/`sin`
     [max_pos, D/2] are float32 device tensors; `positions` is int32 [B].
+    `pe` selects Flux's rotary form instead (flux.applyRope, Tyr/Model/Flux/RoPE.lean:71-96): a
+    float32 [B or 1, max_pos, D/2, 2, 2] table of 2x2 matrices applied to interleaved pairs
+    (the reference's [B, 1, S, D/2, 2, 2] `pe` with its singleton axis dropped).
+    Rows that would fall outside `out` or outside the rotary table are refused here when the
+    position is known on the host (position0); with device-side `positions` the kernel skips
+    them and sets the out-of-range bit of the device status word.
     """
     _require_cuda(x, out)
     if x.dim() != 4 or out.dim() != 4 or x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -400,9 +407,23 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     B, S, H, D = x.shape
     if out.shape[0] != B or out.shape[1] != H or out.shape[3] != D:
         raise ValueError("out does not match x")
-    for t_ in (norm_weight, cos, sin):
+    for t_ in (norm_weight, cos, sin, pe):
         if t_ is not None and (t_.dtype != torch.float32 or not t_.is_contiguous() or not t_.is_cuda):
-            raise ValueError("norm_weight / cos / sin must be contiguous float32 CUDA tensors")
+            raise ValueError("norm_weight / cos / sin / pe must be contiguous float32 CUDA tensors")
+    if pe is not None:
+        if cos is not None or sin is not None:
+            raise ValueError("pass either cos/sin or pe")
+        if pe.dim() != 5 or tuple(pe.shape[2:]) != (D // 2, 2, 2) or pe.shape[0] not in (1, B):
+            raise ValueError("pe must be [B or 1, max_pos, D/2, 2, 2]")
+    cap = out.shape[2]
+    max_pos = pe.shape[1] if pe is not None else (cos.shape[0] if cos is not None else 0)
+    if cos is not None and (sin is None or tuple(cos.shape) != tuple(sin.shape) or cos.dim() != 2 or cos.shape[1] != D // 2):
+        raise ValueError("cos and sin must both be [max_pos, D/2]")
+    if positions is None:
+        if position0 < 0 or position0 + S > cap:
+            raise ValueError(f"rows {position0}..{position0 + S - 1} do not fit the {cap} rows of out")
+        if max_pos and position0 + S > max_pos:
+            raise ValueError(f"positions up to {position0 + S - 1} exceed the {max_pos} rows of the rotary table")
     if positions is not None and (positions.dtype != torch.int32 or not positions.is_cuda):
         raise ValueError("positions must be an int32 CUDA tensor")
     a = PrologueArgs()
@@ -415,6 +436,9 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     a.x_stride[:] = [x.stride(0), x.stride(1), x.stride(2)]
     a.out_stride[:] = [out.stride(0), out.stride(1), out.stride(2)]
     a.eps = float(eps)
+    a.cap, a.max_pos = int(cap), int(max_pos)
+    a.pe = pe.data_ptr() if pe is not None else None
+    a.pe_batch_stride = pe.stride(0) if (pe is not None and pe.shape[0] > 1) else 0
     with torch.cuda.device(x.device):
         check(_lib.load().tyr_b200_attn_qk_prologue(ctypes.byref(a), _stream_ptr(x)))
     return out
@@ -436,6 +460,12 @@ def mergePartials(o_a, lse_a, o_b, lse_b):
 def device_status(device: int = 0, clear: bool = True) -> int:
     """Status word written by the kernels' bounded waits (0 = none gave up)."""
     return int(_lib.load().tyr_b200_attn_device_status(device, int(clear)))
+
+
+def device_check(device: int = 0) -> None:
+    """Raise AttnError if a bounded in-kernel wait gave up or a device-side position or length
+    was out of range since the last check; clears the status word."""
+    check(int(_lib.load().tyr_b200_attn_device_check(device)))
 
 
 def launch_count() -> int:
