@@ -41,10 +41,6 @@ constexpr int kBM = 128;        // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;        // keys per KV tile
 constexpr int kThreads = 384;   // 12 warps
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
-#ifndef TYR_PREFILL_SPLIT
-#define TYR_PREFILL_SPLIT 1
-#endif
-constexpr bool kSplitDefault = TYR_PREFILL_SPLIT != 0;  // half-tile pipelining of the score tiles (see the kernel)
 // Register split.  setmaxnreg only moves registers inside what the CTA was given at
 // launch (threads x the compiled per-thread count, 168 under __launch_bounds__(384, 1));
 // asking for more would block a warp forever, so the sum is checked here.
@@ -85,7 +81,7 @@ struct Cfg {
   static constexpr bool kStageO = (D == 128);
   static constexpr uint32_t kOOff = kVOff + kVStages * kTileBytes;  // one O tile staged for its TMA store
   static constexpr uint32_t kBarOff = kOOff + kTileBytes;
-  static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 4 + 2 + 2 + 2 + 1 + 2 + 2;
+  static constexpr int kNumBars = 2 + 2 + 2 * kKStages + 2 * kVStages + 2 + 2 + 2 + 2 + 1 + 2;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemO = 256;
@@ -103,13 +99,12 @@ struct Bars {
   static constexpr int k_empty = k_full + C::kKStages;    // [KS]
   static constexpr int v_full = k_empty + C::kKStages;    // [VS]
   static constexpr int v_empty = v_full + C::kVStages;    // [VS]
-  static constexpr int s_full = v_empty + C::kVStages;    // [2] S_t in tensor memory; split kernel: [2][2], index 2 t + half
-  static constexpr int p_half = s_full + 4;               // [2] keys 0..63 of P_t written
+  static constexpr int s_full = v_empty + C::kVStages;    // [2] S_t in tensor memory
+  static constexpr int p_half = s_full + 2;               // [2] keys 0..63 of P_t written
   static constexpr int p_full = p_half + 2;               // [2] keys 64..127 of P_t written
   static constexpr int o_full = p_full + 2;               // [2] last PV_t of the item done
   static constexpr int o_staged = o_full + 2;             // an O tile is in the staging buffer (4 warp arrivals)
   static constexpr int o_stage_free = o_staged + 1;       // [2] the TMA store of Q tile t's O has read the buffer
-  static constexpr int pvl_done = o_stage_free + 2;       // [2] split kernel: the first-half PV_t of a KV tile is done
   __device__ static constexpr uint32_t count(int i) {
     return ((i >= p_half && i < p_half + 4) || i == o_staged) ? 4u : 1u;  // one arrival per softmax warp
   }
@@ -188,8 +183,16 @@ __device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
 // tile and stage, and each MMA only adds a compile-time constant to the address field.
 constexpr uint32_t kDescHi = umma_desc_hi(1024);  // 8-row groups of every operand tile are 1024 B apart
 
-template <int D>
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo) {
+struct NoPeek {
+  __device__ __forceinline__ void operator()() const {}
+};
+
+// `peek` runs before the last two MMAs of the group.  An MMA takes about as long to issue as to
+// execute (about 50 cycles against 64), so what the issuing thread asks there, the state of the
+// barrier it will wait on next, is answered by the time the group is issued, and the tensor pipe
+// does not drain behind the latency of a wait that would have succeeded anyway.
+template <int D, class Peek = NoPeek>
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo, Peek peek = Peek()) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, false);
   // Opaque to the optimizer: the per-step descriptors are recomputed at each use instead of
   // being kept (and spilled) as loop invariants of the issuing thread.
@@ -199,27 +202,7 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       const uint32_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
-      if (kb == 0 && ks == 0)
-        umma_ss_lo<0>(s_tmem, q_lo, k_lo, kDescHi, idesc, 0);
-      else
-        umma_ss_lo<1>(s_tmem, q_lo + off, k_lo + off, kDescHi, idesc, 1);
-    }
-  }
-}
-
-// S_t[:, 64 half .. 64 half + 64) = Q_t K_j[64 half .. 64 half + 64)^T: the N = 64 form of the
-// split kernel.  `k_lo` is the descriptor of the whole K tile; rows 64.. of a box start 8 KB in.
-template <int D>
-__device__ __forceinline__ void issue_qk_half(uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo, int half) {
-  constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN / 2, false);
-  k_lo += (half * 64 * 128) >> 4;
-  s_tmem += half * (kBN / 2);
-  asm volatile("" : "+r"(q_lo), "+r"(k_lo));
-#pragma unroll
-  for (int kb = 0; kb < D / 64; ++kb) {
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      const uint32_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
+      if (kb == D / 64 - 1 && ks == 2) peek();
       if (kb == 0 && ks == 0)
         umma_ss_lo<0>(s_tmem, q_lo, k_lo, kDescHi, idesc, 0);
       else
@@ -229,14 +212,15 @@ __device__ __forceinline__ void issue_qk_half(uint32_t s_tmem, uint32_t q_lo, ui
 }
 
 // `half` selects keys [64*half, 64*half + 64) of the tile.
-template <int D>
+template <int D, class Peek = NoPeek>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_lo,
-                                         bool accumulate, int half) {
+                                         bool accumulate, int half, Peek peek = Peek()) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
   asm volatile("" : "+r"(v_lo), "+r"(p_tmem));  // as in issue_qk
 #pragma unroll
   for (int k4 = 0; k4 < kBN / 32; ++k4) {
     const int kk = half * (kBN / 32) + k4;
+    if (k4 == kBN / 32 - 2) peek();
     // 16 keys = two 8-row groups of the V tile; 16 bf16 of P = 8 TMEM columns
     if (k4 == 0)
       umma_ts_lo<-1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, accumulate ? 1u : 0u);
@@ -269,7 +253,7 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
 // previous item's epilogue.
 // kWindow compiles the sliding-window and padding-key masks in (rows may then meet tiles in
 // which they see no key); the plain kernel carries none of those checks.
-template <int D, bool kSplit, bool kWindow>
+template <int D, bool kWindow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -371,157 +355,83 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool ok = true;
         int kc = 0, vc = 0;      // K / V tiles consumed so far
         int pc0 = 0, pc1 = 0;    // P tiles consumed so far, per Q tile
-        if constexpr (kSplit) {
-          // Half-tile pipelining.  The S_t region holds two independent halves (keys 0..63 in
-          // columns 0..63, keys 64..127 in columns 64..127); P of a half overlays the first 32
-          // columns of its own half.  As soon as the softmax warps hand over P of a half, that
-          // half's PV and then the same half of the NEXT tile's scores are issued, so the next
-          // scores of a half are computed while the softmax works on the other half and a
-          // softmax warp never waits for the tensor pipe in the steady state.  (With whole
-          // 128-column tiles the chain P_t(j) -> PV_t(j) -> S_t(j+1) left each softmax warp
-          // idle for about 1300 cycles per KV tile.)  The price is two N = 64 score products
-          // per tile, 48 cycles each per 16 of head_dim instead of 64 for one N = 128.
-          int sc0 = 0, sc1 = 0;  // tile-steps issued so far per Q tile (phases of p_half / p_full)
-          for (int it = 0; ok; ++it) {
-            const int w = snake_item(it, total_items, p.snake);
-            if (w < 0) break;
-            const Item im = decode_item<kWindow>(w, p);
-            const int n0 = im.n0, n1 = im.n1;
-            ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
-                 mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
-            if (!ok) break;
-            tc_fence_after();
-            {
-              const int s = kc % C::kKStages;
-              const uint32_t k_desc = umma_desc_lo(sK + s * C::kTileBytes, 16);
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                issue_qk_half<D>(tS0, q_desc0, k_desc, h);
-                umma_commit(bar(B::s_full + 0 + h));
-                issue_qk_half<D>(tS1, q_desc1, k_desc, h);
-                umma_commit(bar(B::s_full + 2 + h));
-              }
-              if (n0 == 1) umma_commit(bar(B::q_empty + 0));
-              if (n1 == 1) umma_commit(bar(B::q_empty + 1));
-              umma_commit(bar(B::k_empty + s));
-              ++kc;
-            }
-            for (int j = 0; j < n1 && ok; ++j) {
-              const int vs = vc % C::kVStages;
-              const bool next = (j + 1 < n1);
-              const int ks = kc % C::kKStages;
-              ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
-              if (ok && next) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
-              if (!ok) break;
-              const uint32_t v_smem = umma_desc_lo(sV + vs * C::kTileBytes, C::kBoxBytes);
-              const uint32_t k_smem = umma_desc_lo(sK + ks * C::kTileBytes, 16);
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                if (j < n0) {
-                  ok = mbar_wait(bar((h ? B::p_full : B::p_half) + 0), sc0 & 1, abortp);
-                  if (!ok) break;
-                  tc_fence_after();
-                  issue_pv<D>(tO0, tS0 + h * (kBN / 2 - 32), v_smem, j > 0 || h > 0, h);
-                  if (h == 0) umma_commit(bar(B::pvl_done + 0));
-                  if (h == 1 && j == n0 - 1) umma_commit(bar(B::o_full + 0));
-                  if (j + 1 < n0) {
-                    issue_qk_half<D>(tS0, q_desc0, k_smem, h);
-                    umma_commit(bar(B::s_full + 0 + h));
-                    if (h == 1 && j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
-                  }
-                }
-                ok = mbar_wait(bar((h ? B::p_full : B::p_half) + 1), sc1 & 1, abortp);
-                if (!ok) break;
-                tc_fence_after();
-                issue_pv<D>(tO1, tS1 + h * (kBN / 2 - 32), v_smem, j > 0 || h > 0, h);
-                if (h == 0) umma_commit(bar(B::pvl_done + 1));
-                if (h == 1) {
-                  umma_commit(bar(B::v_empty + vs));
-                  if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
-                }
-                if (next) {
-                  issue_qk_half<D>(tS1, q_desc1, k_smem, h);
-                  umma_commit(bar(B::s_full + 2 + h));
-                  if (h == 1) {
-                    if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
-                    umma_commit(bar(B::k_empty + ks));
-                  }
-                }
-              }
-              if (!ok) break;
-              if (j < n0) ++sc0;
-              ++sc1;
-              ++vc;
-              if (next) ++kc;
-            }
+        for (int it = 0; ok; ++it) {
+          const int w = snake_item(it, total_items, p.snake);
+          if (w < 0) break;
+          const Item im = decode_item<kWindow>(w, p);
+          const int n0 = im.n0, n1 = im.n1;
+          ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
+               mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          {
+            const int s = kc % C::kKStages;
+            const uint32_t k_desc = umma_desc_lo(sK + s * C::kTileBytes, 16);
+            issue_qk<D>(tS0, q_desc0, k_desc);
+            umma_commit(bar(B::s_full + 0));
+            if (n0 == 1) umma_commit(bar(B::q_empty + 0));
+            issue_qk<D>(tS1, q_desc1, k_desc);
+            umma_commit(bar(B::s_full + 1));
+            if (n1 == 1) umma_commit(bar(B::q_empty + 1));
+            umma_commit(bar(B::k_empty + s));
+            ++kc;
           }
-        } else {
-          for (int it = 0; ok; ++it) {
-            const int w = snake_item(it, total_items, p.snake);
-            if (w < 0) break;
-            const Item im = decode_item<kWindow>(w, p);
-            const int n0 = im.n0, n1 = im.n1;
-            ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
-                 mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
+          // answers to the next waits, asked from inside the MMA group issued before each of them
+          uint32_t pk = 0;  // bits: 1 V tile landed, 2 K tile landed, 4 / 8 first half / all of P_0 written, 16 / 32 of P_1
+          for (int j = 0; j < n1 && ok; ++j) {
+            const int vs = vc % C::kVStages;
+            const bool next = (j + 1 < n1);
+            const int ks = kc % C::kKStages;
+            if (!(pk & 1u)) ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
+            if (ok && next && !(pk & 2u)) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
+            if (!ok) break;
+            const uint32_t v_smem = umma_desc_lo(sV + vs * C::kTileBytes, C::kBoxBytes);
+            const uint32_t k_smem = umma_desc_lo(sK + ks * C::kTileBytes, 16);
+            if (j < n0) {
+              if (!(pk & 4u)) ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv<D>(tO0, tS0, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 0), pc0 & 1) << 3; });
+              if (!(pk & 8u)) ok = mbar_wait(bar(B::p_full + 0), pc0 & 1, abortp);
+              if (!ok) break;
+              tc_fence_after();
+              if (j + 1 < n0) {
+                issue_pv<D>(tO0, tS0, v_smem, true, 1);
+              } else {  // no score product follows: ask about the other tile's P from here
+                issue_pv<D>(tO0, tS0, v_smem, true, 1, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
+              }
+              ++pc0;
+              if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
+            }
+            if (j + 1 < n0) {
+              issue_qk<D>(tS0, q_desc0, k_smem, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
+              umma_commit(bar(B::s_full + 0));
+              if (j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
+            }
+            if (!(pk & 16u)) ok = mbar_wait(bar(B::p_half + 1), pc1 & 1, abortp);
             if (!ok) break;
             tc_fence_after();
-            {
-              const int s = kc % C::kKStages;
-              const uint32_t k_desc = umma_desc_lo(sK + s * C::kTileBytes, 16);
-              issue_qk<D>(tS0, q_desc0, k_desc);
-              umma_commit(bar(B::s_full + 0));
-              if (n0 == 1) umma_commit(bar(B::q_empty + 0));
-              issue_qk<D>(tS1, q_desc1, k_desc);
+            issue_pv<D>(tO1, tS1, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 1), pc1 & 1) << 5; });
+            if (!(pk & 32u)) ok = mbar_wait(bar(B::p_full + 1), pc1 & 1, abortp);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv<D>(tO1, tS1, v_smem, true, 1);
+            ++pc1;
+            umma_commit(bar(B::v_empty + vs));
+            ++vc;
+            if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
+            if (next) {
+              // the next step starts with three waits and no MMA between them: ask about all three
+              pk = 0;  // every answer of this step has been used
+              issue_qk<D>(tS1, q_desc1, k_smem, [&] {
+                pk = mbar_test(bar(B::v_full + vc % C::kVStages), (vc / C::kVStages) & 1);
+                if (j + 2 < n1) pk |= mbar_test(bar(B::k_full + (kc + 1) % C::kKStages), ((kc + 1) / C::kKStages) & 1) << 1;
+                if (j + 1 < n0) pk |= mbar_test(bar(B::p_half + 0), pc0 & 1) << 2;
+              });
               umma_commit(bar(B::s_full + 1));
-              if (n1 == 1) umma_commit(bar(B::q_empty + 1));
-              umma_commit(bar(B::k_empty + s));
+              if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
+              umma_commit(bar(B::k_empty + ks));
               ++kc;
-            }
-            for (int j = 0; j < n1 && ok; ++j) {
-              const int vs = vc % C::kVStages;
-              const bool next = (j + 1 < n1);
-              const int ks = kc % C::kKStages;
-              ok = mbar_wait(bar(B::v_full + vs), (vc / C::kVStages) & 1, abortp);
-              if (ok && next) ok = mbar_wait(bar(B::k_full + ks), (kc / C::kKStages) & 1, abortp);
-              if (!ok) break;
-              const uint32_t v_smem = umma_desc_lo(sV + vs * C::kTileBytes, C::kBoxBytes);
-              const uint32_t k_smem = umma_desc_lo(sK + ks * C::kTileBytes, 16);
-              if (j < n0) {
-                ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
-                if (!ok) break;
-                tc_fence_after();
-                issue_pv<D>(tO0, tS0, v_smem, j > 0, 0);
-                ok = mbar_wait(bar(B::p_full + 0), pc0 & 1, abortp);
-                if (!ok) break;
-                tc_fence_after();
-                issue_pv<D>(tO0, tS0, v_smem, true, 1);
-                ++pc0;
-                if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
-              }
-              if (j + 1 < n0) {
-                issue_qk<D>(tS0, q_desc0, k_smem);
-                umma_commit(bar(B::s_full + 0));
-                if (j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
-              }
-              ok = mbar_wait(bar(B::p_half + 1), pc1 & 1, abortp);
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv<D>(tO1, tS1, v_smem, j > 0, 0);
-              ok = mbar_wait(bar(B::p_full + 1), pc1 & 1, abortp);
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv<D>(tO1, tS1, v_smem, true, 1);
-              ++pc1;
-              umma_commit(bar(B::v_empty + vs));
-              ++vc;
-              if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
-              if (next) {
-                issue_qk<D>(tS1, q_desc1, k_smem);
-                umma_commit(bar(B::s_full + 1));
-                if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
-                umma_commit(bar(B::k_empty + ks));
-                ++kc;
-              }
             }
           }
         }
@@ -580,210 +490,104 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int n_t = t ? im.n1 : im.n0;
       float m_ref = -INFINITY, l = 0.f;
 
-      if constexpr (kSplit) {
-        // Half-tile pipelining: the 128 keys of a KV tile arrive as two independent 64-column
-        // halves, each with its own "scores ready" barrier; P of a half overlays the first 32
-        // columns of that half.  While this warp works on one half the tensor pipe runs the PV of
-        // the other and that half's scores of the next tile.
-        for (int j = 0; j < n_t; ++j, ++sc) {
+      for (int j = 0; j < n_t; ++j, ++sc) {
+        ok = mbar_wait(bar(B::s_full + t), sc & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[kBN / 32][32];  // the row's scores, raw fp32 bits
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            ok = mbar_wait(bar(B::s_full + 2 * t + h), sc & 1, abortp);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t sr[2][32];  // the row's 64 scores of this half, raw fp32 bits
-            tmem_ld32(tS + h * 64, sr[0]);
-            tmem_ld32(tS + h * 64 + 32, sr[1]);
-            tmem_wait_ld();
-            tmem_ld_ready(sr[0]);
-            tmem_ld_ready(sr[1]);
+        for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, sr[c]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < kBN / 32; ++c) tmem_ld_ready(sr[c]);
 
-            // keys this row may see in this half: [first, limit)
-            const int key0 = (im.lo + j) * kBN + h * 64;
-            int limit = p.kv_seq - key0;
-            if (p.causal) limit = min(limit, row + 1 - key0);
-            const int first = (kWindow && p.window > 0) ? row - p.window + 1 - key0 : 0;
-            if (limit < 64 || first > 0) {
+        // keys this row may see in this tile: [first, limit)
+        const int key0 = (im.lo + j) * kBN;
+        int limit = p.kv_seq - key0;
+        if (p.causal) limit = min(limit, row + 1 - key0);
+        const int first = (kWindow && p.window > 0) ? row - p.window + 1 - key0 : 0;
+        if (limit < kBN || first > 0) {
 #pragma unroll
-              for (int c = 0; c < 64; ++c)
-                if (c >= limit || c < first) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+          for (int c = 0; c < kBN; ++c)
+            if (c >= limit || c < first) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+        }
+        if (kWindow && p.key_mask != nullptr) {
+          // padding keys: lane i fetches the mask bytes of keys 4i..4i+3 of the tile, four
+          // ballots spread them to every row; key c is bit (c >> 2) of ballot (c & 3)
+          const uint8_t* mrow = p.key_mask + im.b * p.key_mask_stride + key0;
+          uint32_t vb[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int kk = 4 * lane + e;
+            const bool valid = (key0 + kk < p.kv_seq) && mrow[kk] != 0;
+            vb[e] = __ballot_sync(0xffffffffu, valid);
+          }
+#pragma unroll
+          for (int c = 0; c < kBN; ++c)
+            if (!((vb[c & 3] >> (c >> 2)) & 1u)) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
+        }
+        float mxa[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 3; i + 1 < 32; i += 2)
+            mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+          mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
+        }
+        const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+
+        const float m_new = fmaxf(m_ref, mx);
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          const bool grow = (m_new - m_ref) * sl2 > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            // PV_t(j-1) has completed (s_full covers it) and PV_t(j) is not issued
+            // before this warp arrives on p_half, so O_t is ours to rescale.
+            // a row that has seen no key yet (m_new still -inf, sliding window only) keeps its zeros
+            const float alpha = (kWindow && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl2);
+            l *= alpha;
+            m_ref = m_new;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_wait_ld();
+              tmem_ld_ready(o);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + c * 32, o);
             }
-            if (kWindow && p.key_mask != nullptr) {
-              // padding keys: lane i fetches the mask bytes of keys 2i, 2i+1 of the half, two
-              // ballots spread them to every row; key c is bit (c >> 1) of ballot (c & 1)
-              const uint8_t* mrow = p.key_mask + im.b * p.key_mask_stride + key0;
-              uint32_t vb[2];
+          }
+        }
+        const float neg = (kWindow && m_ref == -INFINITY) ? 0.0f : -m_ref * sl2;  // all -inf scores give P = 0
+        const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
+        uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int kk = 2 * lane + e;
-                const bool valid = (key0 + kk < p.kv_seq) && mrow[kk] != 0;
-                vb[e] = __ballot_sync(0xffffffffu, valid);
-              }
-#pragma unroll
-              for (int c = 0; c < 64; ++c)
-                if (!((vb[c & 1] >> (c >> 1)) & 1u)) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
-            }
-            float mxa[2];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
-#pragma unroll
-              for (int i = 3; i + 1 < 32; i += 2)
-                mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-              mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
-            }
-            const float m_new = fmaxf(m_ref, fmaxf(mxa[0], mxa[1]));
-            if (j == 0 && h == 0) {
-              m_ref = m_new;
-            } else {
-              const bool grow = (m_new - m_ref) * sl2 > kRescaleThreshold;
-              if (__any_sync(0xffffffffu, grow)) {
-                // O_t may only be touched between two of its PV products.  Everything issued so
-                // far must have completed: for the first half that is PV_t of the previous
-                // tile's second half, which the second-half scores of THIS tile were issued
-                // behind; for the second half it is this tile's first-half PV, which has its
-                // own commit.  The next PV_t is not issued before this warp arrives below.
-                ok = mbar_wait(bar(h == 0 ? B::s_full + 2 * t + 1 : B::pvl_done + t), sc & 1, abortp);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const float alpha = (kWindow && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl2);
-                l *= alpha;
-                m_ref = m_new;
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                  uint32_t o[32];
-                  tmem_ld32(tO + c * 32, o);
-                  tmem_wait_ld();
-                  tmem_ld_ready(o);
-#pragma unroll
-                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                  tmem_st32(tO + c * 32, o);
-                }
-              }
-            }
-            const float neg = (kWindow && m_ref == -INFINITY) ? 0.0f : -m_ref * sl2;  // all -inf scores give P = 0
-            const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
-            uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              uint32_t pk[16];
-              exp_chunk(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
-              tmem_st16(tS + h * 64 + c * 16, pk);
-            }
-            {
-              float s0, s1;
-              unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
-              l += s0 + s1;
-            }
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t pk[16];
+          exp_chunk(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
+          tmem_st16(tS + c * 16, pk);
+          if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar((h ? B::p_full : B::p_half) + t));
+            if (lane == 0) mbar_arrive(bar(B::p_half + t));
           }
-          if (!ok) break;
         }
-      } else {
-        for (int j = 0; j < n_t; ++j, ++sc) {
-          ok = mbar_wait(bar(B::s_full + t), sc & 1, abortp);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          uint32_t sr[kBN / 32][32];  // the row's scores, raw fp32 bits
-  #pragma unroll
-          for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, sr[c]);
-          tmem_wait_ld();
-  #pragma unroll
-          for (int c = 0; c < kBN / 32; ++c) tmem_ld_ready(sr[c]);
-
-          // keys this row may see in this tile: [first, limit)
-          const int key0 = (im.lo + j) * kBN;
-          int limit = p.kv_seq - key0;
-          if (p.causal) limit = min(limit, row + 1 - key0);
-          const int first = (kWindow && p.window > 0) ? row - p.window + 1 - key0 : 0;
-          if (limit < kBN || first > 0) {
-  #pragma unroll
-            for (int c = 0; c < kBN; ++c)
-              if (c >= limit || c < first) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
-          }
-          if (kWindow && p.key_mask != nullptr) {
-            // padding keys: lane i fetches the mask bytes of keys 4i..4i+3 of the tile, four
-            // ballots spread them to every row; key c is bit (c >> 2) of ballot (c & 3)
-            const uint8_t* mrow = p.key_mask + im.b * p.key_mask_stride + key0;
-            uint32_t vb[4];
-  #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int kk = 4 * lane + e;
-              const bool valid = (key0 + kk < p.kv_seq) && mrow[kk] != 0;
-              vb[e] = __ballot_sync(0xffffffffu, valid);
-            }
-  #pragma unroll
-            for (int c = 0; c < kBN; ++c)
-              if (!((vb[c & 3] >> (c >> 2)) & 1u)) sr[c >> 5][c & 31] = 0xff800000u;  // -inf
-          }
-          float mxa[4];
-  #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            mxa[c] = max3_f32(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
-  #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-  #pragma unroll
-            for (int i = 3; i + 1 < 32; i += 2)
-              mxa[c] = max3_f32(mxa[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-            mxa[c] = fmaxf(mxa[c], __uint_as_float(sr[c][31]));
-          }
-          const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
-
-          const float m_new = fmaxf(m_ref, mx);
-          if (j == 0) {
-            m_ref = m_new;
-          } else {
-            const bool grow = (m_new - m_ref) * sl2 > kRescaleThreshold;
-            if (__any_sync(0xffffffffu, grow)) {
-              // PV_t(j-1) has completed (s_full covers it) and PV_t(j) is not issued
-              // before this warp arrives on p_half, so O_t is ours to rescale.
-              // a row that has seen no key yet (m_new still -inf, sliding window only) keeps its zeros
-              const float alpha = (kWindow && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl2);
-              l *= alpha;
-              m_ref = m_new;
-  #pragma unroll
-              for (int c = 0; c < D / 32; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tO + c * 32, o);
-                tmem_wait_ld();
-                tmem_ld_ready(o);
-  #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                tmem_st32(tO + c * 32, o);
-              }
-            }
-          }
-          const float neg = (kWindow && m_ref == -INFINITY) ? 0.0f : -m_ref * sl2;  // all -inf scores give P = 0
-          const uint64_t sl2x2 = pack_f32x2(sl2, sl2), negx2 = pack_f32x2(neg, neg);
-          uint64_t sum_a = pack_f32x2(0.f, 0.f), sum_b = sum_a;
-  #pragma unroll
-          for (int c = 0; c < kBN / 32; ++c) {
-            uint32_t pk[16];
-            exp_chunk(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
-            tmem_st16(tS + c * 16, pk);
-            if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
-              tmem_wait_st();
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(bar(B::p_half + t));
-            }
-          }
-          {
-            float s0, s1;
-            unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
-            l += s0 + s1;
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B::p_full + t));
+        {
+          float s0, s1;
+          unpack_f32x2(add_f32x2(sum_a, sum_b), s0, s1);
+          l += s0 + s1;
         }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B::p_full + t));
       }
       if (!ok) break;
 
@@ -949,7 +753,7 @@ int sm_count() {
   return n;
 }
 
-template <int D, bool kSplit, bool kWindow>
+template <int D, bool kWindow>
 int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   using C = Cfg<D>;
   CUtensorMap tq, tk, tv, to;
@@ -964,7 +768,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
     if (!attr_set[dev].load(std::memory_order_acquire)) {
-      cudaError_t attr_err = cudaFuncSetAttribute(prefill_kernel<D, kSplit, kWindow>,
+      cudaError_t attr_err = cudaFuncSetAttribute(prefill_kernel<D, kWindow>,
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)C::kSmemBytes);
       if (attr_err != cudaSuccess) return (int)attr_err;
@@ -1014,7 +818,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   const long long items = (long long)p.items_per_group * a.n_kv_head * a.batch;
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   const int grid = (int)std::min<long long>(items, sm_count());
-  prefill_kernel<D, kSplit, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
+  prefill_kernel<D, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -1027,9 +831,8 @@ int make_tile_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {
   const bool win = a.window_size > 0 || a.key_mask != nullptr;
-  constexpr bool M = kSplitDefault;
-  if (a.head_dim == 128) return win ? launch<128, M, true>(a, scale, status, st) : launch<128, M, false>(a, scale, status, st);
-  if (a.head_dim == 64) return win ? launch<64, M, true>(a, scale, status, st) : launch<64, M, false>(a, scale, status, st);
+  if (a.head_dim == 128) return win ? launch<128, true>(a, scale, status, st) : launch<128, false>(a, scale, status, st);
+  if (a.head_dim == 64) return win ? launch<64, true>(a, scale, status, st) : launch<64, false>(a, scale, status, st);
   return -TYR_ATTN_ERR_HEAD_DIM;
 }
 

@@ -56,6 +56,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Non-blocking look at a phase: 1 if it has completed.  Used to ask early, from inside a run of
+// instructions that take long to issue, about a barrier that will be waited on right after it.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Default wait limit for any single mbarrier phase, in SM clock cycles (2-4 s at 1-2 GHz).  Far
 // above any legitimate wait (the longest is one KV tile of work, microseconds) and
 // short enough that a protocol error ends the kernel instead of holding the GPU.
