@@ -195,3 +195,80 @@ def test_window_of_one_is_closed_form():
     torch.cuda.synchronize()
     assert torch.equal(d_v, (d_o[:, 0].float() + d_o[:, 1].float()).bfloat16()[:, None])
     assert d_q.float().abs().max().item() < 0.1 and d_k.float().abs().max().item() < 0.1
+
+
+def _block_grads_f64(q, k, v, d_o, b, hkv, j0, j1, causal, scale):
+    """Exact dK, dV of the key block [j0, j1) of (batch b, KV head hkv) and exact dQ of the query rows
+    [j0, j1) of the group's first query head, in float64 with numpy.  The formulas are the backward
+    of Tyr/GPU/Kernels/MhaH100.lean:196-344 (the ones tyr_oracle_sdpa_backward implements); only the
+    query rows that can see the block enter, so the cost stays bounded at any sequence length.
+    q [B,Hq,S,D], k/v [B,Hkv,S,D], d_o like q: float32 numpy arrays (bf16-representable values)."""
+    Hq, Hkv, S, D = q.shape[1], k.shape[1], q.shape[2], q.shape[3]
+    g = Hq // Hkv
+    kk, vv = k[b, hkv].astype(np.float64), v[b, hkv].astype(np.float64)
+    i0 = j0 if causal else 0                       # first query row that sees key j0
+    d_k = np.zeros((j1 - j0, D)); d_v = np.zeros((j1 - j0, D))
+    d_q_first = None
+    for h in range(hkv * g, (hkv + 1) * g):
+        qq, dd = q[b, h, i0:].astype(np.float64), d_o[b, h, i0:].astype(np.float64)
+        s = qq @ kk.T * scale                      # [rows, S]
+        if causal:
+            rows = np.arange(i0, S)[:, None]
+            s = np.where(np.arange(S)[None, :] > rows, -np.inf, s)
+        m = s.max(axis=1, keepdims=True)
+        p = np.exp(s - m)
+        p /= p.sum(axis=1, keepdims=True)
+        o = p @ vv
+        delta = (dd * o).sum(axis=1, keepdims=True)
+        d_s = p * (dd @ vv.T - delta) * scale      # [rows, S]
+        d_v += p[:, j0:j1].T @ dd
+        d_k += d_s[:, j0:j1].T @ qq
+        if h == hkv * g:
+            lo = j0 - i0
+            d_q_first = d_s[lo:lo + (j1 - j0)] @ kk
+    return d_k, d_v, d_q_first
+
+
+def test_block_formulas_agree_with_the_oracle():
+    """The float64 block helper above is pinned to tyr_oracle_sdpa_backward on a small case."""
+    rng = np.random.default_rng(3)
+    bf = lambda a: torch.from_numpy(a.astype(np.float32)).bfloat16().float().numpy()
+    q, k, v, d_o = bf(rng.standard_normal((1, 4, 96, 64))), bf(rng.standard_normal((1, 2, 96, 64))), \
+        bf(rng.standard_normal((1, 2, 96, 64))), bf(rng.standard_normal((1, 4, 96, 64)))
+    for causal in (True, False):
+        w_q, w_k, w_v = c_oracle.sdpa_backward(q, k, v, d_o, causal)
+        d_k, d_v, d_q = _block_grads_f64(q, k, v, d_o, 0, 1, 32, 64, causal, 0.125)
+        assert np.abs(d_k - w_k[0, 1, 32:64]).max() <= 1e-4
+        assert np.abs(d_v - w_v[0, 1, 32:64]).max() <= 1e-4
+        assert np.abs(d_q - w_q[0, 2, 32:64]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["qwen3_0p6b_prefill", "qwen3_8b_prefill"])
+def test_benchmark_shapes_by_sampled_key_blocks_and_rows(name):
+    """The backward at the two sizes it is benchmarked on, checked against exact float64 gradients
+    of sampled 128-key blocks (dK, dV, summed over the whole GQA group) and 128 query rows (dQ)."""
+    from tyr_b200 import nn as tnn
+    from tyr_b200 import workloads as W
+    w = W.WORKLOADS[name]
+    qh, kh, vh = W.make_prefill(w)
+    g = torch.Generator(device="cpu").manual_seed(w.seed + 100)
+    dh = torch.randn(qh.shape, generator=g).bfloat16()
+    q, k, v, d_o = (t.to(_dev()) for t in (qh, kh, vh, dh))
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=w.causal)
+    d_q, d_k, d_v = tnn.attentionBwd(q, k, v, o, lse, d_o, is_causal=w.causal)
+    torch.cuda.synchronize()
+    assert tnn.device_status(0, True) == 0
+    qn, kn, vn, dn = (t.float().numpy() for t in (qh, kh, vh, dh))
+    S = w.seq
+    g_ = w.n_head // w.n_kv_head
+    # the last block (few rows see it), one that ends on the tile before it, and one in the second half
+    picks = [(w.batch - 1, w.n_kv_head - 1, S - 128), (0, 0, S - 384), (w.batch // 2, 1, (S // 2 // 128 + 3) * 128)]
+    scale = 1.0 / np.sqrt(w.head_dim)
+    for b, hkv, j0 in picks:
+        want_k, want_v, want_q = _block_grads_f64(qn, kn, vn, dn, b, hkv, j0, j0 + 128, w.causal, scale)
+        for got, want, what in ((d_k[b, hkv, j0:j0 + 128], want_k, "d_k"), (d_v[b, hkv, j0:j0 + 128], want_v, "d_v"),
+                                (d_q[b, hkv * g_, j0:j0 + 128], want_q, "d_q")):
+            gg = got.float().cpu().numpy()
+            assert np.isfinite(gg).all(), (name, what, b, hkv, j0)
+            err = np.abs(gg - want).max() / max(np.abs(want).max(), 1e-6)
+            assert err <= GRAD_REL_TO_MAX, f"{name} {what} block (b={b}, kv head {hkv}, keys {j0}..): {err:.3e}"

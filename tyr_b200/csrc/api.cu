@@ -27,9 +27,11 @@ constexpr int kMaxHostChunks = 64;
 struct HostStage {  // device staging buffers of the host-buffer call, grown on demand
   void* buf = nullptr;
   size_t bytes = 0;
-  cudaStream_t stream = nullptr;      // host->device copies and the kernels
+  cudaStream_t stream = nullptr;      // host->device copies (one copy engine)
+  cudaStream_t compute = nullptr;     // the kernels
   cudaStream_t out_stream = nullptr;  // device->host copies (the other copy engine)
-  cudaEvent_t done[kMaxHostChunks] = {};  // kernel of chunk i finished
+  cudaEvent_t landed[kMaxHostChunks] = {};  // inputs of chunk i are on the device
+  cudaEvent_t done[kMaxHostChunks] = {};    // kernel of chunk i finished
 };
 HostStage g_stage[kMaxDevices];
 
@@ -339,15 +341,17 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   if (!hs.out_stream &&
       (e = cudaStreamCreateWithFlags(&hs.out_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail((int)e);
-  // Pipeline over (batch, KV-head range) chunks: while chunk i computes and chunk i-1 drains to
-  // the host on the device->host copy engine, chunk i+1 is already arriving on the
-  // host->device one.  In [batch, heads, seq, dim] storage the heads of one batch element are
+  if (!hs.compute && (e = cudaStreamCreateWithFlags(&hs.compute, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail((int)e);
+  // Pipeline over (batch, KV-head range) chunks on three streams: while chunk i computes and
+  // chunk i-1 drains to the host on the device->host copy engine, chunk i+1 is already arriving
+  // on the host->device one.  In [batch, heads, seq, dim] storage the heads of one batch element are
   // contiguous, so a chunk is one contiguous piece of each tensor; the more chunks, the less of
   // each copy direction is left uncovered at the two ends of the pipeline.
   const int g = a->n_head / a->n_kv_head;
   const int per_batch = a->batch >= kMaxHostChunks ? 1 : std::min<int>(a->n_kv_head, kMaxHostChunks / a->batch);
   const int batch_chunks = a->batch >= kMaxHostChunks ? kMaxHostChunks : a->batch;
-  cudaStream_t st = hs.stream, so = hs.out_stream;
+  cudaStream_t st = hs.stream, sc = hs.compute, so = hs.out_stream;
   const char *hq = static_cast<const char*>(a->q), *hk = static_cast<const char*>(a->k),
              *hv = static_cast<const char*>(a->v);
   char* ho = static_cast<char*>(a->o);
@@ -366,9 +370,13 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
       const size_t l_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * lh1, l_len = (per_batch > 1 ? nkv * g : nbat * a->n_head) * lh1;
       if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
         return fail((int)e);
+      if (!hs.landed[c] && (e = cudaEventCreateWithFlags(&hs.landed[c], cudaEventDisableTiming)) != cudaSuccess)
+        return fail((int)e);
       if ((e = cudaMemcpyAsync(base + q_off, hq + q_off, q_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
           (e = cudaMemcpyAsync(base + off_k + k_off, hk + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-          (e = cudaMemcpyAsync(base + off_v + k_off, hv + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+          (e = cudaMemcpyAsync(base + off_v + k_off, hv + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+          (e = cudaEventRecord(hs.landed[c], st)) != cudaSuccess ||
+          (e = cudaStreamWaitEvent(sc, hs.landed[c], 0)) != cudaSuccess)
         return fail((int)e);
       TyrAttnPrefillArgs dc = d;
       dc.batch = (int32_t)nbat;
@@ -381,9 +389,9 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
       dc.v = base + off_v + k_off;
       dc.o = base + off_o + q_off;
       dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + l_off) : nullptr;
-      rc = tyr_b200_attn_prefill(&dc, st);
+      rc = tyr_b200_attn_prefill(&dc, sc);
       if (rc) return fail(rc);
-      if ((e = cudaEventRecord(hs.done[c], st)) != cudaSuccess ||
+      if ((e = cudaEventRecord(hs.done[c], sc)) != cudaSuccess ||
           (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
           (e = cudaMemcpyAsync(ho + q_off, base + off_o + q_off, q_len, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
         return fail((int)e);
@@ -393,6 +401,7 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
     }
   }
   e = cudaStreamSynchronize(so);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(sc);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   return fail((int)e);
 }

@@ -48,13 +48,25 @@ struct DecodeParams {
   int* status;    // per-device status word (out-of-range lengths are reported there)
 };
 
-// Length of sequence b, forced into [0, max_kv_seq]: the workspace and the grid are sized for
-// max_kv_seq, so a longer length would index past both.
-__device__ __forceinline__ int clamped_len(const DecodeParams& p, int b, bool report) {
-  if (!p.kv_lens) return p.max_kv_seq;
-  const int raw = p.kv_lens[b];
-  const int len = min(max(raw, 0), p.max_kv_seq);
-  if (report && (len != raw || raw == 0)) atomicOr(p.status, kStatusOutOfRange);
+// A length outside [1, max_kv_seq] (the workspace and the grid are sized for max_kv_seq, so a
+// longer one would index past both): report it once per sequence, give a sequence without any
+// key a defined row (zeros, LSE = -inf), and return the length forced into [0, max_kv_seq].
+// Kept out of line so that this rare path costs the scan loop no registers.
+template <int D>
+__device__ __noinline__ int bad_length(int raw, int max_kv_seq, bool first_cta_of_row, int* status,
+                                       __nv_bfloat16* o_row0, int64_t o_head_stride, float* lse_row0,
+                                       int head0, int heads_here) {
+  const int len = min(max(raw, 0), max_kv_seq);
+  if (first_cta_of_row) {
+    if (threadIdx.x == 0 && head0 == 0) atomicOr(status, kStatusOutOfRange);
+    if (len == 0) {
+      for (int idx = threadIdx.x; idx < heads_here * D; idx += blockDim.x) {
+        const int head = head0 + idx / D, d = idx % D;
+        o_row0[(int64_t)head * o_head_stride + d] = __float2bfloat16_rn(0.f);
+        if (d == 0 && lse_row0) lse_row0[head] = -INFINITY;
+      }
+    }
+  }
   return len;
 }
 
@@ -102,8 +114,10 @@ struct DCfg {
   static constexpr int kTileBytes = kTileKeys * kRowBytes;
   static constexpr int kStageBytes = 2 * kTileBytes;  // K then V
   static constexpr int kSmemBytes = kStages * kStageBytes;
-  // cross-warp merge reuses the ring: 4 warps x 16 rows x (D + 2) floats
-  static_assert(4 * 16 * (D + 2) * 4 <= kSmemBytes, "merge scratch fits in the ring");
+  // cross-warp merge reuses the ring: 4 warps x 16 rows of D floats, rows padded by 4 floats so that
+  // the eight rows a warp stores at once fall on different banks, + 2 floats of (max, sum) per row
+  static constexpr int kMergeStride = D + 4;
+  static_assert(4 * 16 * (kMergeStride + 2) * 4 <= kSmemBytes, "merge scratch fits in the ring");
 };
 
 // byte offset of 16-byte chunk `c` of row `key` inside a swizzled tile
@@ -119,21 +133,18 @@ decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
 
+  // the merge kernel behind this one may start to become resident (it waits for this grid itself)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x;
   const int hkv = blockIdx.y / p.head_groups;
   const int hg = blockIdx.y % p.head_groups;
   const int b = blockIdx.z;
-  const int len = clamped_len(p, b, split == 0 && threadIdx.x == 0 && blockIdx.y == 0);
+  int len = p.kv_lens ? p.kv_lens[b] : p.max_kv_seq;
+  if (len <= 0 || len > p.max_kv_seq)
+    len = bad_length<D>(len, p.max_kv_seq, split == 0, p.status, p.o + b * p.os[0], p.os[1],
+                        p.lse ? p.lse + (int64_t)b * p.n_head : nullptr, hkv * p.group + hg * 16,
+                        min(16, p.group - hg * 16));
   const int n_chunks = (len + p.chunk_len - 1) / p.chunk_len;
-  if (len == 0 && split == 0) {
-    // no key at all: a defined row (zeros, LSE = -inf) instead of stale memory
-    const int head0 = hkv * p.group + hg * 16, heads_here = min(16, p.group - hg * 16);
-    for (int idx = threadIdx.x; idx < heads_here * D; idx += kThreads) {
-      const int head = head0 + idx / D, d = idx % D;
-      p.o[b * p.os[0] + (int64_t)head * p.os[1] + d] = __float2bfloat16_rn(0.f);
-      if (d == 0 && p.lse) p.lse[(int64_t)b * p.n_head + head] = -INFINITY;
-    }
-  }
   if (split >= n_chunks) return;
   const int key_begin = split * p.chunk_len;
   const int key_end = min(len, key_begin + p.chunk_len);
@@ -289,13 +300,14 @@ decode_kernel(const DecodeParams p) {
   // ---- merge the four warps through shared memory
   cp_async_wait<0>();
   __syncthreads();
-  float* sc_o = reinterpret_cast<float*>(smem);               // [4][16][D]
-  float* sc_ml = sc_o + 4 * 16 * D;                           // [4][16][2]
+  constexpr int kMS = C::kMergeStride;
+  float* sc_o = reinterpret_cast<float*>(smem);               // [4][16][D + 4]
+  float* sc_ml = sc_o + 4 * 16 * kMS;                         // [4][16][2]
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) {
     const int d = n * 8 + t4 * 2;
-    float* r0 = sc_o + (warp * 16 + quad) * D + d;
-    float* r1 = sc_o + (warp * 16 + quad + 8) * D + d;
+    float* r0 = sc_o + (warp * 16 + quad) * kMS + d;
+    float* r1 = sc_o + (warp * 16 + quad + 8) * kMS + d;
     r0[0] = oacc[n][0]; r0[1] = oacc[n][1];
     r1[0] = oacc[n][2]; r1[1] = oacc[n][3];
   }
@@ -317,7 +329,7 @@ decode_kernel(const DecodeParams p) {
       const float mw = sc_ml[(w * 16 + r) * 2];
       const float f = (mw == -INFINITY) ? 0.f : ex2f(mw - M);
       L += sc_ml[(w * 16 + r) * 2 + 1] * f;
-      acc += sc_o[(w * 16 + r) * D + d] * f;
+      acc += sc_o[(w * 16 + r) * kMS + d] * f;
     }
     const int head = head0 + r;
     const float outv = acc / L;
@@ -334,11 +346,15 @@ decode_kernel(const DecodeParams p) {
 }
 
 // One CTA per (query head, sequence): weights w_c = 2^(L_c - max L), O = sum w_c O_c / sum w_c.
+// Launched with programmatic stream serialisation: its CTAs may become resident while the split
+// kernel is still draining, and wait here until that grid has completed and its writes are visible,
+// so the launch latency of this second kernel hides behind the tail of the first.
 template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const DecodeParams p) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int len = clamped_len(p, b, false);
+  const int len = p.kv_lens ? min(max(p.kv_lens[b], 0), p.max_kv_seq) : p.max_kv_seq;
   const int n_chunks = (len + p.chunk_len - 1) / p.chunk_len;
   if (n_chunks <= 1) return;  // the split kernel already wrote the final row
   const int64_t slot0 = ((int64_t)b * p.n_head + head) * p.n_splits;
@@ -382,9 +398,19 @@ int launch_d(const TyrAttnDecodeArgs& a, DecodeParams& p, cudaStream_t st) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (p.n_splits > 1) {
-    decode_merge_kernel<D><<<dim3(a.n_head, a.batch), D, 0, st>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.n_head, a.batch);
+    cfg.blockDim = dim3(D);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, decode_merge_kernel<D>, p);
     count_launch();
-    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
   }
   return (int)e;
 }
