@@ -20,7 +20,11 @@ namespace tyr {
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kHeadsInFlight = 4;  // heads whose loads are issued before the first is used
+// Heads whose loads are issued before the first is used, and CTAs per SM the register budget is
+// held to.  Measured on 16 x 4096 tokens x 8 heads x 128: (4, 1) 5.36 TB/s, (8, 1) 4.31, (4, 3) 5.71,
+// (2, 4) 5.38; streaming load/store hints changed nothing.
+constexpr int kHeadsInFlight = 4;
+constexpr int kMinCtasPerSm = 3;  // 2 for the Flux rotary form, whose 32 table values per lane would spill
 
 struct PrologueParams {
   const __nv_bfloat16* x;
@@ -46,7 +50,7 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
 // head its stores are 512/D consecutive rows of the [batch, head, seq, dim] output.
 // kRot: 0 = no rotary, 1 = rotate-half with cos/sin tables, 2 = interleaved pairs with 2x2 tables.
 template <int D, int kRot>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, kRot == 2 ? 2 : kMinCtasPerSm)
 prologue_kernel(const PrologueParams p) {
   constexpr int kHalf = D / 2;
   constexpr int kLanes = D / 16;          // lanes per token
