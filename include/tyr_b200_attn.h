@@ -251,6 +251,9 @@ typedef struct TyrAttnPrologueArgs {
   int32_t max_pos;          /* rows of cos / sin / pe; > 0 when a rotary table is given */
   const float* pe;          /* Flux-style [max_pos, head_dim/2, 2, 2] fp32 table or NULL */
   int64_t pe_batch_stride;  /* elements between the tables of two batch elements (0: shared) */
+  int32_t out_at_row0;      /* != 0: pos_b + s selects the rotary row only and the result is written at
+                               row s of out (a query of a decode step: rotated at the sequence's
+                               position, stored as row 0 of a [batch, heads, seq, head_dim] tensor) */
 } TyrAttnPrologueArgs;
 
 int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* args, void* stream);

@@ -38,8 +38,8 @@ def test_struct_sizes_match_the_c_layout():
     assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
     # 10 pointers, uint64, 6 int32, 24 int64, int32 int32 float int32, pointer, int64
     assert ctypes.sizeof(_lib.BackwardArgs) == 10 * 8 + 8 + 6 * 4 + 24 * 8 + 4 * 4 + 8 + 8
-    # 6 pointers, 5 int32 (+4 padding), 6 int64, float int32 int32 (+4 padding), pointer, int64
-    assert ctypes.sizeof(_lib.PrologueArgs) == 6 * 8 + 5 * 4 + 4 + 6 * 8 + 3 * 4 + 4 + 8 + 8
+    # 6 pointers, 5 int32 (+4 padding), 6 int64, float int32 int32 (+4 padding), pointer, int64, int32 (+4)
+    assert ctypes.sizeof(_lib.PrologueArgs) == 6 * 8 + 5 * 4 + 4 + 6 * 8 + 3 * 4 + 4 + 8 + 8 + 4 + 4
 
 
 def test_arguments_are_rejected_before_any_launch(built_lib):

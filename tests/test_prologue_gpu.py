@@ -171,3 +171,20 @@ def test_many_heads_and_ragged_token_count():
         out = torch.zeros(B, H, S + 2, D, dtype=torch.bfloat16, device=DEV)
         tnn.qkPrologue(x.to(DEV), out, w.to(DEV), cos.to(DEV), sin.to(DEV), position0=2)
         close(out, ref)
+
+
+def test_query_of_a_decode_step_is_rotated_at_its_position_and_stored_at_row_zero():
+    g = torch.Generator(device="cpu").manual_seed(29)
+    B, H, D, max_pos = 3, 4, 128, 64
+    x = torch.randn(B, 1, H, D, generator=g).bfloat16()
+    w = torch.rand(D, generator=g) + 0.5
+    cos, sin = rope_tables(max_pos, D)
+    pos = torch.tensor([0, 17, 63], dtype=torch.int32)
+    # oracle: write each sequence at its own position of a tall tensor, then read that row
+    tall = np.zeros((B, H, max_pos, D), np.float32)
+    c_oracle.qk_prologue(x.float().numpy(), tall, w.numpy(), cos.numpy(), sin.numpy(), positions=pos.numpy())
+    ref = np.stack([tall[b, :, int(pos[b])] for b in range(B)])[:, :, None, :]
+    out = torch.zeros(B, H, 1, D, dtype=torch.bfloat16, device=DEV)
+    tnn.qkPrologue(x.to(DEV), out, w.to(DEV), cos.to(DEV), sin.to(DEV), positions=pos.to(DEV), out_at_row0=True)
+    close(out, ref)
+    assert tnn.device_status(0, True) == 0

@@ -59,7 +59,7 @@ class PrologueArgs(ctypes.Structure):
         ("x", vp), ("out", vp), ("norm_weight", vp), ("cos", vp), ("sin", vp), ("positions", vp),
         ("position0", c_i32), ("batch", c_i32), ("seq", c_i32), ("n_head", c_i32), ("head_dim", c_i32),
         ("x_stride", c_i64 * 3), ("out_stride", c_i64 * 3), ("eps", c_f32),
-        ("cap", c_i32), ("max_pos", c_i32), ("pe", vp), ("pe_batch_stride", c_i64),
+        ("cap", c_i32), ("max_pos", c_i32), ("pe", vp), ("pe_batch_stride", c_i64), ("out_at_row0", c_i32),
     ]
 
 

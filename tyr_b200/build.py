@@ -11,7 +11,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libtyr_b200_attn.so")
 SOURCES = ["api.cu", "prefill_sm100.cu", "backward_sm100.cu", "decode_splitkv.cu", "check_fp32.cu", "qk_prologue.cu",
            "stalled_wait.cu"]
-HEADERS = ["ptx_sm100.cuh", "attn_internal.h", os.path.join("..", "..", "include", "tyr_b200_attn.h")]
+HEADERS = ["ptx_sm100.cuh", "mma_sync.cuh", "attn_internal.h", os.path.join("..", "..", "include", "tyr_b200_attn.h")]
 
 # The reference's own nvcc flags for GPU=B200 (cc/Makefile:66-76) minus fast-math
 # (the kernels ask for approximate ex2/lg2 explicitly where they want them) and

@@ -246,8 +246,9 @@ int tyr_b200_attn_qk_prologue(const TyrAttnPrologueArgs* a, void* stream) {
   // every written row and every rotary row must exist: the reference guards its append with
   // `cache.seq < cache.maxLen` (Tyr/Model/Qwen/Attention.lean:189)
   if (a->cap <= 0 || ((a->cos || a->pe) && a->max_pos <= 0)) return -TYR_ATTN_ERR_SHAPE;
+  if (a->out_at_row0 && a->seq > a->cap) return -TYR_ATTN_ERR_RANGE;
   if (!a->positions) {
-    if ((int64_t)a->position0 + a->seq > a->cap) return -TYR_ATTN_ERR_RANGE;
+    if (!a->out_at_row0 && (int64_t)a->position0 + a->seq > a->cap) return -TYR_ATTN_ERR_RANGE;
     if ((a->cos || a->pe) && (int64_t)a->position0 + a->seq > a->max_pos) return -TYR_ATTN_ERR_RANGE;
   }
   if (!aligned16(a->x) || !aligned16(a->out) || (a->norm_weight && !aligned16(a->norm_weight)) ||

@@ -31,7 +31,7 @@ struct PrologueParams {
   __nv_bfloat16* out;
   const float *w, *cs, *sn, *pe;
   const int32_t* positions;
-  int position0, batch, seq, n_head, d, cap, max_pos;
+  int position0, batch, seq, n_head, d, cap, max_pos, out_at_row0;
   int64_t xs[3], os[3], pe_bs;
   float eps;
   int* status;
@@ -65,7 +65,8 @@ prologue_kernel(const PrologueParams p) {
   const int b = (int)(tt / p.seq);
   const int64_t pos = (int64_t)(p.positions ? p.positions[b] : p.position0) + s;  // output row and rotary row
   // a row outside the cache or the rotary table is skipped and reported, never written
-  const bool in_range = pos >= 0 && pos < p.cap && (kRot == 0 || pos < p.max_pos);
+  const int64_t out_row = p.out_at_row0 ? s : pos;
+  const bool in_range = pos >= 0 && out_row < p.cap && (kRot == 0 || pos < p.max_pos);
   if (live && !in_range && k8 == 0) atomicOr(p.status, kStatusOutOfRange);
   const bool store = live && in_range;
   const int64_t pos_ld = in_range ? pos : 0;
@@ -89,7 +90,7 @@ prologue_kernel(const PrologueParams p) {
   }
 
   const __nv_bfloat16* xt = p.x + b * p.xs[0] + s * p.xs[1];
-  __nv_bfloat16* ot = p.out + b * p.os[0] + pos_ld * p.os[2];
+  __nv_bfloat16* ot = p.out + b * p.os[0] + (in_range ? out_row : 0) * p.os[2];
 
   for (int h0 = 0; h0 < p.n_head; h0 += kHeadsInFlight) {
     uint4 raw_a[kHeadsInFlight], raw_c[kHeadsInFlight];
@@ -179,7 +180,7 @@ int launch_qk_prologue(const TyrAttnPrologueArgs& a, int* status, cudaStream_t s
   p.positions = a.positions;
   p.position0 = a.position0;
   p.batch = a.batch; p.seq = a.seq; p.n_head = a.n_head; p.d = a.head_dim;
-  p.cap = a.cap; p.max_pos = a.max_pos;
+  p.cap = a.cap; p.max_pos = a.max_pos; p.out_at_row0 = a.out_at_row0;
   for (int i = 0; i < 3; ++i) { p.xs[i] = a.x_stride[i]; p.os[i] = a.out_stride[i]; }
   p.eps = a.eps;
   p.status = status;

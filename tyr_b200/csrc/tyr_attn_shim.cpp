@@ -372,12 +372,14 @@ extern "C" lean_object* lean_launch_tyrB200AttnDecodeRagged(b_lean_obj_arg q_, b
 // one-pass form of applyHeadNorm / rotary.applyRotaryEmb / transpose_for_attention /
 // data.sliceScatter (Tyr/Model/Qwen/Attention.lean:73-98, 132-144, 189-193).  `norm_weight_`, `cos_`,
 // `sin_` are float32 CUDA tensors, `positions_` int32 [batch]; any of them may be a tensor with no
-// elements to skip that step (positions: `position0` is used for every sequence).
+// elements to skip that step (positions: `position0` is used for every sequence).  `out_at_row0` != 0:
+// the position selects the rotary row only and the result is written at rows 0.. of out (the query of
+// a decode step).
 extern "C" lean_object* lean_launch_tyrB200QkPrologue(b_lean_obj_arg x_, b_lean_obj_arg out_,
                                                       b_lean_obj_arg norm_weight_, b_lean_obj_arg cos_,
                                                       b_lean_obj_arg sin_, b_lean_obj_arg positions_,
-                                                      uint64_t position0, double eps, uint64_t stream,
-                                                      lean_object* /*w*/) {
+                                                      uint64_t position0, double eps, uint8_t out_at_row0,
+                                                      uint64_t stream, lean_object* /*w*/) {
   try {
     auto x = borrowTensor(x_), out = borrowTensor(out_), w = borrowTensor(norm_weight_),
          cs = borrowTensor(cos_), sn = borrowTensor(sin_), pos = borrowTensor(positions_);
@@ -414,6 +416,7 @@ extern "C" lean_object* lean_launch_tyrB200QkPrologue(b_lean_obj_arg x_, b_lean_
     a.eps = (float)eps;
     a.cap = (int32_t)out.size(2);
     a.max_pos = rot ? (int32_t)cs.size(0) : 0;
+    a.out_at_row0 = out_at_row0 ? 1 : 0;
     int rc = tyr_b200_attn_qk_prologue(&a, reinterpret_cast<void*>(stream));
     if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
     return lean_io_result_mk_ok(lean_box(0));

@@ -42,11 +42,13 @@ opaque tyrB200AttnDecodeRagged.launch
 
 /-- Fused head norm + rotary + layout change + in-place cache append for one projected tensor
     (`x : [batch, seq, heads, headDim]` into `out : [batch, heads, cap, headDim]` at rows
-    `positions[b] + s`).  Tensors with no elements skip a step.  C side: `lean_launch_tyrB200QkPrologue`. -/
+    `positions[b] + s`; with `outAtRow0 = 1` the position selects the rotary row only and the rows are
+    written from row 0, the query of a decode step).  Tensors with no elements skip a step.
+    C side: `lean_launch_tyrB200QkPrologue`. -/
 @[extern "lean_launch_tyrB200QkPrologue"]
 opaque tyrB200QkPrologue.launch
     (x out normWeight cos sin positions : @& Tensor) (position0 : UInt64) (eps : Float)
-    (stream : Tyr.GPU.CudaStream) : IO Unit
+    (outAtRow0 : UInt8) (stream : Tyr.GPU.CudaStream) : IO Unit
 
 /-- LSE merge of two partial attention results over disjoint key sets (`ringAttnReduce`).
     C side: `lean_launch_tyrB200AttnMerge`. -/

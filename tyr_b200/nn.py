@@ -386,7 +386,7 @@ def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
                cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
                positions: Optional[torch.Tensor] = None, position0: int = 0, eps: float = 1e-6,
-               pe: Optional[torch.Tensor] = None):
+               pe: Optional[torch.Tensor] = None, out_at_row0: bool = False):
     """Fused per-head RMSNorm + rotary embedding + [B,S,H,D] -> [B,H,S,D] layout change,
     written into `out` [B,H,cap,D] at rows positions[b] + s (in place: a KV-cache append
     when `out` is the cache).  One pass instead of applyHeadNorm
@@ -397,6 +397,8 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     `pe` selects Flux's rotary form instead (flux.applyRope, Tyr/Model/Flux/RoPE.lean:71-96): a
     float32 [B or 1, max_pos, D/2, 2, 2] table of 2x2 matrices applied to interleaved pairs
     (the reference's [B, 1, S, D/2, 2, 2] `pe` with its singleton axis dropped).
+    `out_at_row0`: the position selects the rotary row only and the result goes to rows 0..S-1 of
+    `out` (the query of a decode step: rotated at each sequence's position, stored as row 0).
     Rows that would fall outside `out` or outside the rotary table are refused here when the
     position is known on the host (position0); with device-side `positions` the kernel skips
     them and sets the out-of-range bit of the device status word.
@@ -419,8 +421,10 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     max_pos = pe.shape[1] if pe is not None else (cos.shape[0] if cos is not None else 0)
     if cos is not None and (sin is None or tuple(cos.shape) != tuple(sin.shape) or cos.dim() != 2 or cos.shape[1] != D // 2):
         raise ValueError("cos and sin must both be [max_pos, D/2]")
+    if out_at_row0 and S > cap:
+        raise ValueError(f"{S} rows do not fit the {cap} rows of out")
     if positions is None:
-        if position0 < 0 or position0 + S > cap:
+        if position0 < 0 or (not out_at_row0 and position0 + S > cap):
             raise ValueError(f"rows {position0}..{position0 + S - 1} do not fit the {cap} rows of out")
         if max_pos and position0 + S > max_pos:
             raise ValueError(f"positions up to {position0 + S - 1} exceed the {max_pos} rows of the rotary table")
@@ -436,7 +440,7 @@ def qkPrologue(x: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.T
     a.x_stride[:] = [x.stride(0), x.stride(1), x.stride(2)]
     a.out_stride[:] = [out.stride(0), out.stride(1), out.stride(2)]
     a.eps = float(eps)
-    a.cap, a.max_pos = int(cap), int(max_pos)
+    a.cap, a.max_pos, a.out_at_row0 = int(cap), int(max_pos), int(bool(out_at_row0))
     a.pe = pe.data_ptr() if pe is not None else None
     a.pe_batch_stride = pe.stride(0) if (pe is not None and pe.shape[0] > 1) else 0
     with torch.cuda.device(x.device):
