@@ -9,7 +9,10 @@ call, although the array keeps whatever the previous call left in it.
 import pytest
 import torch
 
+import numpy as np
+
 from conftest import LSE_REL, O_MAX_ABS
+from oracle import c_oracle
 from tyr_b200 import _lib, nn as tnn
 
 pytestmark = pytest.mark.gpu
@@ -28,6 +31,18 @@ def make_case(lens, seed, n_head=8, n_kv_head=2, d=128):
     return q, tnn.DecodePlan(ks, vs, n_head)
 
 
+def assert_oracle(q, plan, o, lse):
+    """The result of the allocation-free entry against the CPU oracle, sequence by sequence."""
+    ks, vs = plan._keep
+    for b in range(q.shape[0]):
+        Hq, D = q.shape[1], q.shape[2]
+        ro, rl = c_oracle.sdpa(q[b].float().cpu().numpy().reshape(1, Hq, 1, D), ks[b].float().cpu().numpy()[None],
+                               vs[b].float().cpu().numpy()[None], False)
+        assert np.abs(o[b].float().cpu().numpy() - ro[0, :, 0]).max() <= O_MAX_ABS
+        err = np.abs(lse[b].cpu().numpy() - rl[0, :, 0]) / np.maximum(np.abs(rl[0, :, 0]), 1.0)
+        assert err.max() <= LSE_REL
+
+
 def assert_same(o, lse, ro, rlse):
     assert not torch.isnan(o.float()).any()
     assert (o.float() - ro.float()).abs().max().item() <= O_MAX_ABS
@@ -40,12 +55,14 @@ def test_static_scratch_decode_matches_workspace_decode_twice_in_a_row():
     ref1 = tnn.flashDecode(q1, plan1)
     got1 = tnn.flashDecodeStatic(q1, plan1)
     assert_same(*got1, *ref1)
+    assert_oracle(q1, plan1, *got1)
     # call 2, straight after, other data and other chunk counts: stale partials of
     # call 1 are still in the array and must not leak into the result
     q2, plan2 = make_case([2500, 300, 6000], seed=2, n_head=16, n_kv_head=4)
     got2 = tnn.flashDecodeStatic(q2, plan2)
     ref2 = tnn.flashDecode(q2, plan2)
     assert_same(*got2, *ref2)
+    assert_oracle(q2, plan2, *got2)
     # and the first case again gives the first answer again
     got1b = tnn.flashDecodeStatic(q1, plan1)
     assert torch.equal(got1b[0], got1[0]) and torch.equal(got1b[1], got1[1])
