@@ -192,7 +192,7 @@ struct NoPeek {
 // barrier it will wait on next, is answered by the time the group is issued, and the tensor pipe
 // does not drain behind the latency of a wait that would have succeeded anyway.
 template <int D, class Peek = NoPeek>
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo, Peek peek = Peek()) {
+__device__ __forceinline__ void issue_qk(uint32_t issue, uint32_t s_tmem, uint32_t q_lo, uint32_t k_lo, Peek peek = Peek()) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN, false);
   // Opaque to the optimizer: the per-step descriptors are recomputed at each use instead of
   // being kept (and spilled) as loop invariants of the issuing thread.
@@ -204,16 +204,16 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_lo, uint32_
       const uint32_t off = (kb * Cfg<D>::kBoxBytes + ks * 32) >> 4;
       if (kb == D / 64 - 1 && ks == 2) peek();
       if (kb == 0 && ks == 0)
-        umma_ss_lo<0>(s_tmem, q_lo, k_lo, kDescHi, idesc, 0);
+        umma_ss_lo_p<0>(s_tmem, q_lo, k_lo, kDescHi, idesc, 0, issue);
       else
-        umma_ss_lo<1>(s_tmem, q_lo + off, k_lo + off, kDescHi, idesc, 1);
+        umma_ss_lo_p<1>(s_tmem, q_lo + off, k_lo + off, kDescHi, idesc, 1, issue);
     }
   }
 }
 
 // `half` selects keys [64*half, 64*half + 64) of the tile.
 template <int D, class Peek = NoPeek>
-__device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_lo,
+__device__ __forceinline__ void issue_pv(uint32_t issue, uint32_t o_tmem, uint32_t p_tmem, uint32_t v_lo,
                                          bool accumulate, int half, Peek peek = Peek()) {
   constexpr uint32_t idesc = umma_idesc_bf16(kBM, D, true);
   asm volatile("" : "+r"(v_lo), "+r"(p_tmem));  // as in issue_qk
@@ -223,9 +223,9 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint3
     if (k4 == kBN / 32 - 2) peek();
     // 16 keys = two 8-row groups of the V tile; 16 bf16 of P = 8 TMEM columns
     if (k4 == 0)
-      umma_ts_lo<-1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, accumulate ? 1u : 0u);
+      umma_ts_lo_p<-1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, accumulate ? 1u : 0u, issue);
     else
-      umma_ts_lo<1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, 1);
+      umma_ts_lo_p<1>(o_tmem, p_tmem + kk * 8, v_lo + ((kk * 2048) >> 4), kDescHi, idesc, 1, issue);
   }
 }
 
@@ -347,7 +347,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     } else if (warp == 1) {
       // -------------------------------------------------------- MMA issuer
-      if (lane == 0) {
+      // The whole warp runs this loop, convergent; one elected lane issues the MMAs and commits.
+      {
+        const uint32_t issue = elect_one();
         const uint32_t tS0 = tmem + C::kTmemS, tS1 = tS0 + kBN;
         const uint32_t tO0 = tmem + C::kTmemO, tO1 = tO0 + D;
         const uint32_t q_desc0 = umma_desc_lo(sQ, 16);
@@ -367,13 +369,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           {
             const int s = kc % C::kKStages;
             const uint32_t k_desc = umma_desc_lo(sK + s * C::kTileBytes, 16);
-            issue_qk<D>(tS0, q_desc0, k_desc);
-            umma_commit(bar(B::s_full + 0));
-            if (n0 == 1) umma_commit(bar(B::q_empty + 0));
-            issue_qk<D>(tS1, q_desc1, k_desc);
-            umma_commit(bar(B::s_full + 1));
-            if (n1 == 1) umma_commit(bar(B::q_empty + 1));
-            umma_commit(bar(B::k_empty + s));
+            issue_qk<D>(issue, tS0, q_desc0, k_desc);
+            umma_commit_p(bar(B::s_full + 0), issue);
+            if (n0 == 1) umma_commit_p(bar(B::q_empty + 0), issue);
+            issue_qk<D>(issue, tS1, q_desc1, k_desc);
+            umma_commit_p(bar(B::s_full + 1), issue);
+            if (n1 == 1) umma_commit_p(bar(B::q_empty + 1), issue);
+            umma_commit_p(bar(B::k_empty + s), issue);
             ++kc;
           }
           // answers to the next waits, asked from inside the MMA group issued before each of them
@@ -391,46 +393,46 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (!(pk & 4u)) ok = mbar_wait(bar(B::p_half + 0), pc0 & 1, abortp);
               if (!ok) break;
               tc_fence_after();
-              issue_pv<D>(tO0, tS0, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 0), pc0 & 1) << 3; });
+              issue_pv<D>(issue, tO0, tS0, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 0), pc0 & 1) << 3; });
               if (!(pk & 8u)) ok = mbar_wait(bar(B::p_full + 0), pc0 & 1, abortp);
               if (!ok) break;
               tc_fence_after();
               if (j + 1 < n0) {
-                issue_pv<D>(tO0, tS0, v_smem, true, 1);
+                issue_pv<D>(issue, tO0, tS0, v_smem, true, 1);
               } else {  // no score product follows: ask about the other tile's P from here
-                issue_pv<D>(tO0, tS0, v_smem, true, 1, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
+                issue_pv<D>(issue, tO0, tS0, v_smem, true, 1, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
               }
               ++pc0;
-              if (j == n0 - 1) umma_commit(bar(B::o_full + 0));
+              if (j == n0 - 1) umma_commit_p(bar(B::o_full + 0), issue);
             }
             if (j + 1 < n0) {
-              issue_qk<D>(tS0, q_desc0, k_smem, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
-              umma_commit(bar(B::s_full + 0));
-              if (j + 1 == n0 - 1) umma_commit(bar(B::q_empty + 0));
+              issue_qk<D>(issue, tS0, q_desc0, k_smem, [&] { pk |= mbar_test(bar(B::p_half + 1), pc1 & 1) << 4; });
+              umma_commit_p(bar(B::s_full + 0), issue);
+              if (j + 1 == n0 - 1) umma_commit_p(bar(B::q_empty + 0), issue);
             }
             if (!(pk & 16u)) ok = mbar_wait(bar(B::p_half + 1), pc1 & 1, abortp);
             if (!ok) break;
             tc_fence_after();
-            issue_pv<D>(tO1, tS1, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 1), pc1 & 1) << 5; });
+            issue_pv<D>(issue, tO1, tS1, v_smem, j > 0, 0, [&] { pk |= mbar_test(bar(B::p_full + 1), pc1 & 1) << 5; });
             if (!(pk & 32u)) ok = mbar_wait(bar(B::p_full + 1), pc1 & 1, abortp);
             if (!ok) break;
             tc_fence_after();
-            issue_pv<D>(tO1, tS1, v_smem, true, 1);
+            issue_pv<D>(issue, tO1, tS1, v_smem, true, 1);
             ++pc1;
-            umma_commit(bar(B::v_empty + vs));
+            umma_commit_p(bar(B::v_empty + vs), issue);
             ++vc;
-            if (j == n1 - 1) umma_commit(bar(B::o_full + 1));
+            if (j == n1 - 1) umma_commit_p(bar(B::o_full + 1), issue);
             if (next) {
               // the next step starts with three waits and no MMA between them: ask about all three
               pk = 0;  // every answer of this step has been used
-              issue_qk<D>(tS1, q_desc1, k_smem, [&] {
+              issue_qk<D>(issue, tS1, q_desc1, k_smem, [&] {
                 pk = mbar_test(bar(B::v_full + vc % C::kVStages), (vc / C::kVStages) & 1);
                 if (j + 2 < n1) pk |= mbar_test(bar(B::k_full + (kc + 1) % C::kKStages), ((kc + 1) / C::kKStages) & 1) << 1;
                 if (j + 1 < n0) pk |= mbar_test(bar(B::p_half + 0), pc0 & 1) << 2;
               });
-              umma_commit(bar(B::s_full + 1));
-              if (j + 1 == n1 - 1) umma_commit(bar(B::q_empty + 1));
-              umma_commit(bar(B::k_empty + ks));
+              umma_commit_p(bar(B::s_full + 1), issue);
+              if (j + 1 == n1 - 1) umma_commit_p(bar(B::q_empty + 1), issue);
+              umma_commit_p(bar(B::k_empty + ks), issue);
               ++kc;
             }
           }
