@@ -97,7 +97,7 @@ constexpr uint32_t kBwdDescHi = umma_desc_hi(1024);
 
 // score-shaped product: D[128 x 128] = A[128 x D] B[128 x D]^T, both K-major in shared memory
 template <int D>
-__device__ __forceinline__ void issue_nt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+__device__ __forceinline__ void issue_nt(uint32_t issue, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
   constexpr uint32_t idesc = umma_idesc_bf16(kT, kT, false);
   asm volatile("" : "+r"(a_lo), "+r"(b_lo));  // recomputed per use: keeps the issuer's registers few
 #pragma unroll
@@ -106,17 +106,17 @@ __device__ __forceinline__ void issue_nt(uint32_t d_tmem, uint32_t a_lo, uint32_
     for (int ks = 0; ks < 4; ++ks) {
       const uint32_t off = (kb * BCfg<D>::kBoxBytes + ks * 32) >> 4;
       if (kb == 0 && ks == 0)
-        umma_ss_lo<0>(d_tmem, a_lo, b_lo, kBwdDescHi, idesc, 0);
+        umma_ss_lo_p<0>(d_tmem, a_lo, b_lo, kBwdDescHi, idesc, 0, issue);
       else
-        umma_ss_lo<1>(d_tmem, a_lo + off, b_lo + off, kBwdDescHi, idesc, 1);
+        umma_ss_lo_p<1>(d_tmem, a_lo + off, b_lo + off, kBwdDescHi, idesc, 1, issue);
     }
   }
 }
 // accumulating product: D[128 x D] (+)= A[128 x 128 bf16, tensor memory] B[128 x D], B MN-major.
 // `part` 0 / 1: the first / second 64 of the 128 reduction steps only; -1: all of them.
 template <int D>
-__device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool accumulate,
-                                          int part = -1) {
+__device__ __forceinline__ void issue_acc(uint32_t issue, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                          bool accumulate, int part = -1) {
   constexpr uint32_t idesc = umma_idesc_bf16(kT, D, true);
   asm volatile("" : "+r"(b_lo), "+r"(a_tmem));
   const int k0 = part == 1 ? kT / 32 : 0, k1 = part == 0 ? kT / 32 : kT / 16;
@@ -125,9 +125,9 @@ __device__ __forceinline__ void issue_acc(uint32_t d_tmem, uint32_t a_tmem, uint
     if (kk < k0 || kk >= k1) continue;
     // 16 rows of B = two 8-row groups of the tile; 16 bf16 of A = 8 TMEM columns
     if (kk == 0)
-      umma_ts_lo<-1>(d_tmem, a_tmem, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u);
+      umma_ts_lo_p<-1>(d_tmem, a_tmem, b_lo, kBwdDescHi, idesc, accumulate ? 1u : 0u, issue);
     else
-      umma_ts_lo<1>(d_tmem, a_tmem + kk * 8, b_lo + ((kk * 2048) >> 4), kBwdDescHi, idesc, 1);
+      umma_ts_lo_p<1>(d_tmem, a_tmem + kk * 8, b_lo + ((kk * 2048) >> 4), kBwdDescHi, idesc, 1, issue);
   }
 }
 
@@ -249,7 +249,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // the whole warp runs the loop, convergent; one elected lane issues the MMAs and commits
+    {
+      const uint32_t issue = elect_one();
       const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP;
       const uint32_t tA1 = tmem + C::kTmemAcc1, tA2 = tmem + C::kTmemAcc2;
       const uint32_t res1_lo = umma_desc_lo(base + C::kRes1, 16), res2_lo = umma_desc_lo(base + C::kRes2, 16);
@@ -258,9 +260,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
         if (!mbar_wait(bar(C::str_full + s), (g / C::kStages) & 1, abortp)) return false;
         tc_fence_after();
-        issue_nt<D>(tS, res1_lo, umma_desc_lo(t1, 16));
-        issue_nt<D>(tDP, res2_lo, umma_desc_lo(t1 + C::kTileBytes, 16));
-        umma_commit(bar(C::s_full));
+        issue_nt<D>(issue, tS, res1_lo, umma_desc_lo(t1, 16));
+        issue_nt<D>(issue, tDP, res2_lo, umma_desc_lo(t1 + C::kTileBytes, 16));
+        umma_commit_p(bar(C::s_full), issue);
         return true;
       };
       bool ok = true;
@@ -272,7 +274,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (w.n_iter == 0) continue;
         ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
         if (ok) ok = scores(it);
-        if (ok && w.n_iter == 1) umma_commit(bar(C::res_empty));
+        if (ok && w.n_iter == 1) umma_commit_p(bar(C::res_empty), issue);
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           const int s = it % C::kStages;
           const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
@@ -285,21 +287,21 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           if (!ok) break;
           tc_fence_after();
           const uint32_t q_mn = umma_desc_lo(t1, C::kBoxBytes), do_mn = umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes);
-          issue_acc<D>(tA1, tDP, q_mn, i > 0, 0);   // dK += dS^T Q
-          issue_acc<D>(tA2, tS, do_mn, i > 0, 0);   // dV += P^T dO
+          issue_acc<D>(issue, tA1, tDP, q_mn, i > 0, 0);   // dK += dS^T Q
+          issue_acc<D>(issue, tA2, tS, do_mn, i > 0, 0);   // dV += P^T dO
           ok = mbar_wait(bar(C::p_full), it & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          issue_acc<D>(tA1, tDP, q_mn, true, 1);
-          issue_acc<D>(tA2, tS, do_mn, true, 1);
-          umma_commit(bar(C::str_empty + s));
+          issue_acc<D>(issue, tA1, tDP, q_mn, true, 1);
+          issue_acc<D>(issue, tA2, tS, do_mn, true, 1);
+          umma_commit_p(bar(C::str_empty + s), issue);
           if (i + 1 < w.n_iter) {
             ok = scores(it + 1);
             // K and V are read by the score products only: after the unit's last pair of them
             // the producer may fetch the next unit's
-            if (ok && i + 2 == w.n_iter) umma_commit(bar(C::res_empty));
+            if (ok && i + 2 == w.n_iter) umma_commit_p(bar(C::res_empty), issue);
           } else {
-            umma_commit(bar(C::acc_full));
+            umma_commit_p(bar(C::acc_full), issue);
           }
         }
         ++rc;
@@ -603,7 +605,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // the whole warp runs the loop, convergent; one elected lane issues the MMAs and commits
+    {
+      const uint32_t issue = elect_one();
       const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP, tAcc = tmem + C::kTmemAcc;
       const uint32_t q_lo = umma_desc_lo(base + C::kQ, 16), do_lo = umma_desc_lo(base + C::kDO, 16);
       auto scores = [&](int g) {  // S = Q K^T, dP = dO V^T for streamed pair number g; V is free afterwards
@@ -611,10 +615,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!mbar_wait(bar(C::k_full + ks), (g / C::kKStages) & 1, abortp)) return false;
         if (!mbar_wait(bar(C::v_full + vs), (g / C::kVStages) & 1, abortp)) return false;
         tc_fence_after();
-        issue_nt<D>(tS, q_lo, umma_desc_lo(base + C::kK + ks * C::kTileBytes, 16));
-        issue_nt<D>(tDP, do_lo, umma_desc_lo(base + C::kV + vs * C::kTileBytes, 16));
-        umma_commit(bar(C::s_full));
-        umma_commit(bar(C::v_empty + vs));
+        issue_nt<D>(issue, tS, q_lo, umma_desc_lo(base + C::kK + ks * C::kTileBytes, 16));
+        issue_nt<D>(issue, tDP, do_lo, umma_desc_lo(base + C::kV + vs * C::kTileBytes, 16));
+        umma_commit_p(bar(C::s_full), issue);
+        umma_commit_p(bar(C::v_empty + vs), issue);
         return true;
       };
       bool ok = true;
@@ -627,14 +631,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // S and dP of the previous unit's last pair must be in the elementwise warps' registers
         if (ok && it > 0) ok = mbar_wait(bar(C::sdp_free), (it - 1) & 1, abortp);
         if (ok) ok = scores(it);
-        if (ok && w.n_iter == 1) umma_commit(bar(C::res_empty));
+        if (ok && w.n_iter == 1) umma_commit_p(bar(C::res_empty), issue);
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           if (i + 1 < w.n_iter) {
             // S(i) and dP(i) are in the elementwise warps' registers: the next pair may overwrite them
             ok = mbar_wait(bar(C::sdp_free), it & 1, abortp);
             if (ok) ok = scores(it + 1);
             if (!ok) break;
-            if (i + 2 == w.n_iter) umma_commit(bar(C::res_empty));  // Q and dO are read by score products only
+            if (i + 2 == w.n_iter) umma_commit_p(bar(C::res_empty), issue);  // Q and dO are read by score products only
           }
           ok = mbar_wait(bar(C::p_full + (it & 1)), (it >> 1) & 1, abortp);
           // the unit's first dQ product overwrites the accumulator the previous epilogue reads
@@ -642,11 +646,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
           const int ks = it % C::kKStages;
-          issue_acc<D>(tAcc, tmem + C::kTmemDS + (it & 1) * 64,
+          issue_acc<D>(issue, tAcc, tmem + C::kTmemDS + (it & 1) * 64,
                        umma_desc_lo(base + C::kK + ks * C::kTileBytes, C::kBoxBytes), i > 0);
-          umma_commit(bar(C::k_empty + ks));
+          umma_commit_p(bar(C::k_empty + ks), issue);
         }
-        if (ok) umma_commit(bar(C::acc_full));
+        if (ok) umma_commit_p(bar(C::acc_full), issue);
       }
     }
   } else if (warp >= 4) {

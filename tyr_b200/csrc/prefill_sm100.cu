@@ -41,6 +41,7 @@ constexpr int kBM = 128;        // query rows per tile (= TMEM lanes)
 constexpr int kBN = 128;        // keys per KV tile
 constexpr int kThreads = 384;   // 12 warps
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
+constexpr int kExpPolyPairs = 2;           // of every 8 column pairs, computed on the FMA pipe (see exp_chunk)
 // Register split.  setmaxnreg only moves registers inside what the CTA was given at
 // launch (threads x the compiled per-thread count, 168 under __launch_bounds__(384, 1));
 // asking for more would block a warp forever, so the sum is checked here.
@@ -229,18 +230,54 @@ __device__ __forceinline__ void issue_pv(uint32_t issue, uint32_t o_tmem, uint32
   }
 }
 
-// exp2 of one 32-column chunk of a score row, packed to bf16x2, with the row sum in fp32.
+// 2^t for a pair of scores on the FMA pipe instead of the special-function unit: t = n + f with
+// n = round(t) taken from the mantissa of t + 1.5 * 2^23, a cubic through the Chebyshev nodes of
+// [-0.5, 0.5] for 2^f (relative error 1.0e-4, below the 3.9e-3 step of the bf16 value P is rounded
+// to), then n added to the exponent.  t is clamped at -125 so the exponent never wraps: a masked
+// score (-inf) gives 2^-125 instead of 0, which is why the masked-row instantiation (a row may see
+// no key at all and must then come out as NaN, like ATen's) does not use it.
+__device__ __forceinline__ void ex2_poly_pair(uint64_t t2, float& p0, float& p1) {
+  float t0, t1;
+  unpack_f32x2(t2, t0, t1);
+  t0 = fmaxf(t0, -125.f);
+  t1 = fmaxf(t1, -125.f);
+  const uint64_t tc = pack_f32x2(t0, t1);
+  const uint64_t r = add_f32x2(tc, pack_f32x2(12582912.f, 12582912.f));  // low mantissa bits = round(t)
+  const uint64_t n = add_f32x2(r, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = add_f32x2(tc, n ^ 0x8000000080000000ull);
+  uint64_t q = fma_f32x2(pack_f32x2(0.05583828315f, 0.05583828315f), f, pack_f32x2(0.2426394820f, 0.2426394820f));
+  q = fma_f32x2(q, f, pack_f32x2(0.6931367517f, 0.6931367517f));
+  q = fma_f32x2(q, f, pack_f32x2(0.9999245405f, 0.9999245405f));
+  uint32_t pb0, pb1, rb0, rb1;
+  unpack_u32x2(q, pb0, pb1);
+  unpack_u32x2(r, rb0, rb1);
+  p0 = __uint_as_float(pb0 + (rb0 << 23));
+  p1 = __uint_as_float(pb1 + (rb1 << 23));
+}
+
+// exp2 of one 32-column chunk of a score row, packed to bf16x2, with the row sum in fp32.  kPoly of
+// every 8 column pairs take the FMA-pipe polynomial, the rest ex2.approx.  With the MMA issuer
+// running ahead of the tensor pipe the softmax warps are what bounds a KV tile, and a quarter of
+// the exponentials off the special-function unit is the measured optimum (2 of 8: +6 % on the
+// long-sequence workloads; 3 of 8 starts to spill and loses).
 // (Measured and left out: ex2.approx.ftz.bf16x2 / ex2.approx.f16x2 take 16 cycles per warp
 // instruction on the special-function unit against 8 for the f32 form, so packing two scores
-// into one op gains nothing; a cubic on the FMA pipe for part of the columns lost as well.)
+// into one op gains nothing.)
+template <int kPoly>
 __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2x2, uint64_t negx2,
                                           uint32_t (&pk)[16], uint64_t& sum_a, uint64_t& sum_b) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * i], sr[2 * i + 1]), sl2x2, negx2);
-    float t0, t1;
-    unpack_f32x2(t2, t0, t1);
-    const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+    float p0, p1;
+    if ((i & 7) < kPoly) {
+      ex2_poly_pair(t2, p0, p1);
+    } else {
+      float t0, t1;
+      unpack_f32x2(t2, t0, t1);
+      p0 = ex2_approx(t0);
+      p1 = ex2_approx(t1);
+    }
     if (i & 1) sum_b = add_f32x2(sum_b, pack_f32x2(p0, p1));
     else sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
     pk[i] = pack_bf16x2(p0, p1);
@@ -572,7 +609,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) {
           uint32_t pk[16];
-          exp_chunk(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
+          exp_chunk<kWindow ? 0 : kExpPolyPairs>(sr[c], sl2x2, negx2, pk, sum_a, sum_b);
           tmem_st16(tS + c * 16, pk);
           if (c == 1) {  // keys 0..63 of P are in tensor memory: the first half of PV may start
             tmem_wait_st();
