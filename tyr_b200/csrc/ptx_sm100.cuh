@@ -449,4 +449,29 @@ __device__ __forceinline__ float max3_f32(float a, float b, float c) {
   return d;
 }
 
+// 2^t for a pair of scores on the FMA pipe instead of the special-function unit: t = n + f with
+// n = round(t) taken from the mantissa of t + 1.5 * 2^23, a cubic through the Chebyshev nodes of
+// [-0.5, 0.5] for 2^f (relative error 1.0e-4, below the 3.9e-3 step of the bf16 value P is rounded
+// to), then n added to the exponent.  t is clamped at -125 so the exponent never wraps: a masked
+// score (-inf) gives 2^-125 instead of 0, which is why the masked-row instantiation of the forward (a
+// row may see no key at all and must then come out as NaN, like ATen's) does not use it.
+__device__ __forceinline__ void ex2_poly_pair(uint64_t t2, float& p0, float& p1) {
+  float t0, t1;
+  unpack_f32x2(t2, t0, t1);
+  t0 = fmaxf(t0, -125.f);
+  t1 = fmaxf(t1, -125.f);
+  const uint64_t tc = pack_f32x2(t0, t1);
+  const uint64_t r = add_f32x2(tc, pack_f32x2(12582912.f, 12582912.f));  // low mantissa bits = round(t)
+  const uint64_t n = add_f32x2(r, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = add_f32x2(tc, n ^ 0x8000000080000000ull);
+  uint64_t q = fma_f32x2(pack_f32x2(0.05583828315f, 0.05583828315f), f, pack_f32x2(0.2426394820f, 0.2426394820f));
+  q = fma_f32x2(q, f, pack_f32x2(0.6931367517f, 0.6931367517f));
+  q = fma_f32x2(q, f, pack_f32x2(0.9999245405f, 0.9999245405f));
+  uint32_t pb0, pb1, rb0, rb1;
+  unpack_u32x2(q, pb0, pb1);
+  unpack_u32x2(r, rb0, rb1);
+  p0 = __uint_as_float(pb0 + (rb0 << 23));
+  p1 = __uint_as_float(pb1 + (rb1 << 23));
+}
+
 }  // namespace tyr
