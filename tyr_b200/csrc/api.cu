@@ -23,7 +23,8 @@ std::mutex g_host_mu;  // serialises the host-buffer call and guards g_stage
 DeviceState g_state[kMaxDevices];
 std::atomic<uint64_t> g_launches{0};
 
-constexpr int kMaxHostChunks = 64;
+constexpr int kHostChunks = 4;            // pieces the host-buffer call aims for (its two end pieces are halved)
+constexpr int kMaxHostChunks = kHostChunks + 2;
 struct HostStage {  // device staging buffers of the host-buffer call, grown on demand
   void* buf = nullptr;
   size_t bytes = 0;
@@ -347,11 +348,37 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   // Pipeline over (batch, KV-head range) chunks on three streams: while chunk i computes and
   // chunk i-1 drains to the host on the device->host copy engine, chunk i+1 is already arriving
   // on the host->device one.  In [batch, heads, seq, dim] storage the heads of one batch element are
-  // contiguous, so a chunk is one contiguous piece of each tensor; the more chunks, the less of
-  // each copy direction is left uncovered at the two ends of the pipeline.
+  // contiguous, so a chunk is one contiguous piece of each tensor.  What the pipeline cannot cover
+  // is the first chunk's way in and the last chunk's kernel and way out, so those two chunks are
+  // halved; against that every piece costs copy-engine and launch time (five copies, a kernel on a
+  // slice of the grid), and few pieces win: Qwen3-8B-shaped (403 MB in, 272 MB out) 10.9 ms as one
+  // or two pieces, 9.0 ms with 4 to 8 (+2 for the halved ends), 9.4 with 16, 10.9 with 32 or 64; the
+  // smaller workloads are fastest at 4 as well.  9.0 ms is the 403 MB at the 45 GB/s the link
+  // gives each direction while both are busy.
   const int g = a->n_head / a->n_kv_head;
-  const int per_batch = a->batch >= kMaxHostChunks ? 1 : std::min<int>(a->n_kv_head, kMaxHostChunks / a->batch);
-  const int batch_chunks = a->batch >= kMaxHostChunks ? kMaxHostChunks : a->batch;
+  const int per_batch = a->batch >= kHostChunks ? 1 : std::min<int>(a->n_kv_head, kHostChunks / a->batch);
+  const int batch_chunks = a->batch >= kHostChunks ? kHostChunks : a->batch;
+  struct Piece { int b0, b1, h0, h1; };  // batch elements [b0, b1) x KV heads [h0, h1); heads partial only when b1 = b0 + 1
+  Piece pieces[kMaxHostChunks];
+  int n_pieces = 0;
+  for (int bc = 0; bc < batch_chunks; ++bc) {
+    const int b0 = (int)((long long)a->batch * bc / batch_chunks), b1 = (int)((long long)a->batch * (bc + 1) / batch_chunks);
+    for (int hc = 0; hc < per_batch; ++hc) {
+      const int h0 = (int)((long long)a->n_kv_head * hc / per_batch), h1 = (int)((long long)a->n_kv_head * (hc + 1) / per_batch);
+      const bool end = (bc == 0 && hc == 0) || (bc == batch_chunks - 1 && hc == per_batch - 1);
+      if (end && b1 - b0 == 1 && h1 - h0 >= 2) {
+        const int hm = (h0 + h1) / 2;
+        pieces[n_pieces++] = {b0, b1, h0, hm};
+        pieces[n_pieces++] = {b0, b1, hm, h1};
+      } else if (end && b1 - b0 >= 2) {
+        const int bm = (b0 + b1) / 2;
+        pieces[n_pieces++] = {b0, bm, 0, a->n_kv_head};
+        pieces[n_pieces++] = {bm, b1, 0, a->n_kv_head};
+      } else {
+        pieces[n_pieces++] = {b0, b1, h0, h1};
+      }
+    }
+  }
   cudaStream_t st = hs.stream, sc = hs.compute, so = hs.out_stream;
   const char *hq = static_cast<const char*>(a->q), *hk = static_cast<const char*>(a->k),
              *hv = static_cast<const char*>(a->v);
@@ -359,47 +386,43 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   const size_t qh1 = (size_t)a->q_seq * a->head_dim * es;   // one query head of one batch element
   const size_t kh1 = (size_t)a->kv_seq * a->head_dim * es;  // one KV head
   const size_t lh1 = (size_t)a->q_seq * 4;
-  int c = 0;
-  for (int bc = 0; bc < batch_chunks; ++bc) {
-    const int b0 = (int)((long long)a->batch * bc / batch_chunks), b1 = (int)((long long)a->batch * (bc + 1) / batch_chunks);
-    for (int hc = 0; hc < per_batch; ++hc, ++c) {
-      const int h0 = (int)((long long)a->n_kv_head * hc / per_batch), h1 = (int)((long long)a->n_kv_head * (hc + 1) / per_batch);
-      // per_batch > 1 only with one batch element per chunk, so the piece stays contiguous
-      const size_t nbat = (size_t)(b1 - b0), nkv = (size_t)(h1 - h0);
-      const size_t q_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * qh1, q_len = (per_batch > 1 ? nkv * g : nbat * a->n_head) * qh1;
-      const size_t k_off = ((size_t)b0 * a->n_kv_head + h0) * kh1, k_len = (per_batch > 1 ? nkv : nbat * a->n_kv_head) * kh1;
-      const size_t l_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * lh1, l_len = (per_batch > 1 ? nkv * g : nbat * a->n_head) * lh1;
-      if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
-        return fail((int)e);
-      if (!hs.landed[c] && (e = cudaEventCreateWithFlags(&hs.landed[c], cudaEventDisableTiming)) != cudaSuccess)
-        return fail((int)e);
-      if ((e = cudaMemcpyAsync(base + q_off, hq + q_off, q_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-          (e = cudaMemcpyAsync(base + off_k + k_off, hk + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-          (e = cudaMemcpyAsync(base + off_v + k_off, hv + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
-          (e = cudaEventRecord(hs.landed[c], st)) != cudaSuccess ||
-          (e = cudaStreamWaitEvent(sc, hs.landed[c], 0)) != cudaSuccess)
-        return fail((int)e);
-      TyrAttnPrefillArgs dc = d;
-      dc.batch = (int32_t)nbat;
-      if (per_batch > 1) {
-        dc.n_kv_head = (int32_t)nkv;
-        dc.n_head = (int32_t)(nkv * g);
-      }
-      dc.q = base + q_off;
-      dc.k = base + off_k + k_off;
-      dc.v = base + off_v + k_off;
-      dc.o = base + off_o + q_off;
-      dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + l_off) : nullptr;
-      rc = tyr_b200_attn_prefill(&dc, sc);
-      if (rc) return fail(rc);
-      if ((e = cudaEventRecord(hs.done[c], sc)) != cudaSuccess ||
-          (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
-          (e = cudaMemcpyAsync(ho + q_off, base + off_o + q_off, q_len, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
-        return fail((int)e);
-      if (a->lse && (e = cudaMemcpyAsync(reinterpret_cast<char*>(a->lse) + l_off, base + off_l + l_off, l_len,
-                                         cudaMemcpyDeviceToHost, so)) != cudaSuccess)
-        return fail((int)e);
+  for (int c = 0; c < n_pieces; ++c) {
+    const int b0 = pieces[c].b0, b1 = pieces[c].b1, h0 = pieces[c].h0, h1 = pieces[c].h1;
+    const bool part = (h1 - h0) < a->n_kv_head;  // some of the KV heads of one batch element
+    const size_t nbat = (size_t)(b1 - b0), nkv = (size_t)(h1 - h0);
+    const size_t q_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * qh1, q_len = (part ? nkv * g : nbat * a->n_head) * qh1;
+    const size_t k_off = ((size_t)b0 * a->n_kv_head + h0) * kh1, k_len = (part ? nkv : nbat * a->n_kv_head) * kh1;
+    const size_t l_off = ((size_t)b0 * a->n_head + (size_t)h0 * g) * lh1, l_len = (part ? nkv * g : nbat * a->n_head) * lh1;
+    if (!hs.done[c] && (e = cudaEventCreateWithFlags(&hs.done[c], cudaEventDisableTiming)) != cudaSuccess)
+      return fail((int)e);
+    if (!hs.landed[c] && (e = cudaEventCreateWithFlags(&hs.landed[c], cudaEventDisableTiming)) != cudaSuccess)
+      return fail((int)e);
+    if ((e = cudaMemcpyAsync(base + q_off, hq + q_off, q_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(base + off_k + k_off, hk + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(base + off_v + k_off, hv + k_off, k_len, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaEventRecord(hs.landed[c], st)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(sc, hs.landed[c], 0)) != cudaSuccess)
+      return fail((int)e);
+    TyrAttnPrefillArgs dc = d;
+    dc.batch = (int32_t)nbat;
+    if (part) {
+      dc.n_kv_head = (int32_t)nkv;
+      dc.n_head = (int32_t)(nkv * g);
     }
+    dc.q = base + q_off;
+    dc.k = base + off_k + k_off;
+    dc.v = base + off_v + k_off;
+    dc.o = base + off_o + q_off;
+    dc.lse = d.lse ? reinterpret_cast<float*>(base + off_l + l_off) : nullptr;
+    rc = tyr_b200_attn_prefill(&dc, sc);
+    if (rc) return fail(rc);
+    if ((e = cudaEventRecord(hs.done[c], sc)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(so, hs.done[c], 0)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(ho + q_off, base + off_o + q_off, q_len, cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+      return fail((int)e);
+    if (a->lse && (e = cudaMemcpyAsync(reinterpret_cast<char*>(a->lse) + l_off, base + off_l + l_off, l_len,
+                                       cudaMemcpyDeviceToHost, so)) != cudaSuccess)
+      return fail((int)e);
   }
   e = cudaStreamSynchronize(so);
   if (e == cudaSuccess) e = cudaStreamSynchronize(sc);
