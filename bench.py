@@ -488,9 +488,13 @@ def run_ours(args):
     from tyr_b200 import partition as P
     rank, world, local = dist_env()
     world = max(world, 1)
+    solo = args.shard_of is not None
+    if solo:  # one rank's shard of an N-way job, alone on one GPU and without a process group
+        rank, world = (int(x) for x in args.shard_of.split("/"))
+        assert 0 <= rank < world
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    use_dist = world > 1
+    use_dist = world > 1 and not solo
     if use_dist:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -585,7 +589,7 @@ def run_ours(args):
     check_rows(par, qg, kg, vg, w.causal, oh, lseh, sh.batch[0], sh.kv_heads[0] * g_, 8, w.seed + 5, f"{w.name}@host-call")
 
     sharded = None
-    if use_dist and not args.no_others:
+    if (use_dist or solo) and not args.no_others:
         del sets
         sharded = sharded_workloads(tnn, dev, rank, world, barrier, all_max, par)
 
@@ -616,7 +620,7 @@ def run_ours(args):
     if not par.ok:
         print(f"rank {rank}: PARITY MISS {par.where[:8]}", file=sys.stderr, flush=True)
 
-    if rank == 0:
+    if rank == 0 or solo:
         psum = par.summary()
         psum["ok"], psum["rows"] = parity_ok, rows_total
         psum["ranks_checked"] = world
@@ -650,6 +654,10 @@ def run_ours(args):
             line["other_workloads"] = others
         if sharded is not None:
             line["strong_scaling_sharded"] = sharded
+        if solo:
+            line["shard_of"] = {"rank": rank, "world": world,
+                                "note": "this rank's shard alone on one GPU: value = whole-job work over this shard's time"}
+            line["parity"]["ranks_checked"] = 1
         print(json.dumps(line), flush=True)
     if use_dist:
         dist.barrier()
@@ -670,6 +678,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=[n for n, w in W.WORKLOADS.items() if w.kind == "prefill"])
     ap.add_argument("--no-others", action="store_true", help="skip the extra kernel-only workloads")
+    ap.add_argument("--shard-of", default=None, metavar="R/N",
+                    help="run rank R's shard of an N-GPU job alone on one GPU (no process group): its time and parity")
     ap.add_argument("--profile", choices=["prefill", "backward", "decode", "prologue"], default=None,
                     help="profiler-friendly run: only warm-up + steps of one kernel, no e2e/CPU legs")
     ap.add_argument("--decode-batch", type=int, default=None, help="sequences of the decode workload (profile runs)")
