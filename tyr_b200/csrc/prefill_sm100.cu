@@ -48,6 +48,31 @@ constexpr int kExpPolyPairs = 2;           // of every 8 column pairs, computed 
 constexpr int kLaunchRegs = 168, kCtrlRegs = 88, kSoftmaxRegs = 208;
 static_assert(128 * kCtrlRegs + 256 * kSoftmaxRegs <= kThreads * kLaunchRegs, "register pool of the CTA");
 
+// Division of a non-negative 32-bit number by a divisor fixed per launch, as a multiply-high and a
+// shift: q = umulhi(n, mul) >> shr with mul = ceil(2^(31 + ceil(log2 d)) / d), exact for n < 2^31.
+// Every role decodes its item index at every item boundary; the hardware has no integer divider,
+// and seven emulated divisions are about a thousand cycles on the path between two items.
+struct FastDiv {
+  uint32_t mul, shr, d;
+  __device__ __forceinline__ int div(int n) const {
+    return d == 1u ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
+  }
+};
+inline FastDiv make_fastdiv(int d) {
+  FastDiv f;
+  f.d = static_cast<uint32_t>(std::max(d, 1));
+  f.mul = 0;
+  f.shr = 0;
+  if (f.d > 1u) {
+    int lg = 0;
+    while ((1ull << lg) < f.d) ++lg;  // ceil(log2 d)
+    const int pw = 31 + lg;
+    f.mul = static_cast<uint32_t>(((1ull << pw) + f.d - 1) / f.d);
+    f.shr = static_cast<uint32_t>(pw - 32);
+  }
+  return f;
+}
+
 struct PrefillParams {
   __nv_bfloat16* o;
   int64_t o_stride_b, o_stride_h, o_stride_s;
@@ -65,6 +90,11 @@ struct PrefillParams {
   float scale_log2;           // scale * log2(e)
   int* status;
   long long wait_limit;  // cycles any single barrier wait may take before the CTA gives up
+  // the item decode's divisors in multiply-high form (decode_item<., true>)
+  int heads_per_level;        // items per row block per (batch, KV head): group, or group / 2 when pairing heads
+  FastDiv by_chunk_items;     // / (groups_per_chunk * items_per_group)
+  FastDiv by_level_full, by_level_last;  // / (groups in the chunk * heads_per_level), full chunks and the last one
+  FastDiv by_heads_per_level, by_kv_heads;
 };
 
 template <int D>
@@ -128,31 +158,54 @@ struct Item {
 //  heads : the same 128 rows of two query heads that share a KV head (GQA).  Both tiles
 //          then visit exactly the same K/V tiles, so under a causal mask neither waits
 //          for the other's extra diagonal tile, and a short query block wastes no slot.
-template <bool kWindow>
+// kFast: the divisions as multiply-high (FastDiv).  The D=64 instantiations take it: their
+// workloads are short items (the char-level GPT shape has 2.6 items of 1-2 KV tiles per CTA, and
+// the decode sat on the path between them: 24.4 -> 22.7 us).  With the long items of the D=128
+// workloads nothing is gained at the boundary, and that form of this function measured 3 % slower
+// there (1113 vs 1154 TFLOP/s, either order), so they keep the plain divisions.
+template <bool kWindow, bool kFast>
 __device__ __forceinline__ Item decode_item(int w, const PrefillParams& p) {
   Item it;
   const int n_groups = p.batch * p.n_kv_head;
-  const int items_per_group = p.items_per_group;
-  const int heads_per_level = p.pair_heads ? p.group / 2 : p.group;  // items per row block per group
-  const int chunk = w / (p.groups_per_chunk * items_per_group);
-  const int within = w - chunk * p.groups_per_chunk * items_per_group;
-  const int g0 = chunk * p.groups_per_chunk;
-  const int groups_here = min(p.groups_per_chunk, n_groups - g0);
-  const int per_level = groups_here * heads_per_level;
-  it.mblk = p.n_mblk - 1 - within / per_level;
-  const int idx = within % per_level;
-  const int gi = g0 + idx / heads_per_level;
-  it.b = gi / p.n_kv_head;
-  it.hkv = gi % p.n_kv_head;
+  int hl;  // item within the row block of its group
+  if (kFast) {
+    const int chunk = p.by_chunk_items.div(w);
+    const int within = w - chunk * static_cast<int>(p.by_chunk_items.d);
+    const int g0 = chunk * p.groups_per_chunk;
+    const bool full = n_groups - g0 >= p.groups_per_chunk;
+    const FastDiv& by_level = full ? p.by_level_full : p.by_level_last;
+    const int level = by_level.div(within);
+    it.mblk = p.n_mblk - 1 - level;
+    const int idx = within - level * static_cast<int>(by_level.d);
+    const int gl = p.by_heads_per_level.div(idx);
+    hl = idx - gl * p.heads_per_level;
+    const int gi = g0 + gl;
+    it.b = p.by_kv_heads.div(gi);
+    it.hkv = gi - it.b * p.n_kv_head;
+  } else {
+    const int items_per_group = p.items_per_group;
+    const int heads_per_level = p.pair_heads ? p.group / 2 : p.group;  // items per row block per group
+    const int chunk = w / (p.groups_per_chunk * items_per_group);
+    const int within = w - chunk * p.groups_per_chunk * items_per_group;
+    const int g0 = chunk * p.groups_per_chunk;
+    const int groups_here = min(p.groups_per_chunk, n_groups - g0);
+    const int per_level = groups_here * heads_per_level;
+    it.mblk = p.n_mblk - 1 - within / per_level;
+    const int idx = within % per_level;
+    const int gi = g0 + idx / heads_per_level;
+    it.b = gi / p.n_kv_head;
+    it.hkv = gi % p.n_kv_head;
+    hl = idx % heads_per_level;
+  }
   const int nkv_total = (p.kv_seq + kBN - 1) / kBN;
   int last0, last1;  // last KV tile (exclusive) under a causal mask
   if (p.pair_heads) {
-    it.hq[0] = it.hkv * p.group + 2 * (idx % heads_per_level);
+    it.hq[0] = it.hkv * p.group + 2 * hl;
     it.hq[1] = it.hq[0] + 1;
     it.row[0] = it.row[1] = it.mblk * kBM;
     last0 = last1 = it.mblk + 1;
   } else {
-    it.hq[0] = it.hq[1] = it.hkv * p.group + idx % heads_per_level;
+    it.hq[0] = it.hq[1] = it.hkv * p.group + hl;
     it.row[0] = it.mblk * 2 * kBM;
     it.row[1] = it.row[0] + kBM;
     last0 = 2 * it.mblk + 1;  // top-left causal: a tile needs the keys up to its last row
@@ -317,7 +370,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow>(w, p);
+          const Item im = decode_item<kWindow, D == 64>(w, p);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (it > 0) ok = ok && mbar_wait(bar(B::q_empty + t), (it - 1) & 1, abortp);
@@ -372,7 +425,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow>(w, p);
+          const Item im = decode_item<kWindow, D == 64>(w, p);
           const int n0 = im.n0, n1 = im.n1;
           ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
                mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
@@ -463,7 +516,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow>(w, p);
+          const Item im = decode_item<kWindow, D == 64>(w, p);
 #pragma unroll
           for (int t = 0; t < 2; ++t, ++u) {
             ok = mbar_wait(bar(B::o_staged), u & 1, abortp);
@@ -498,7 +551,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int it = 0; ok; ++it) {
       const int w = snake_item(it, total_items, p.snake);
       if (w < 0) break;
-      const Item im = decode_item<kWindow>(w, p);
+      const Item im = decode_item<kWindow, D == 64>(w, p);
       const int row = (t ? im.row[1] : im.row[0]) + r;  // query index
       const int hq = t ? im.hq[1] : im.hq[0];
       const int n_t = t ? im.n1 : im.n0;
@@ -815,6 +868,13 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
     const long long g = all_fit ? n_groups : std::max<long long>((48ll << 20) / group_bytes, 1);
     p.groups_per_chunk = (int)std::min<long long>(g, n_groups);
     p.snake = all_fit ? 1 : 0;
+    p.heads_per_level = p.pair_heads ? (a.n_head / a.n_kv_head) / 2 : a.n_head / a.n_kv_head;
+    const int groups_last = (int)(n_groups % p.groups_per_chunk);
+    p.by_chunk_items = make_fastdiv(p.groups_per_chunk * p.items_per_group);
+    p.by_level_full = make_fastdiv(p.groups_per_chunk * p.heads_per_level);
+    p.by_level_last = make_fastdiv(std::max(groups_last, 1) * p.heads_per_level);
+    p.by_heads_per_level = make_fastdiv(p.heads_per_level);
+    p.by_kv_heads = make_fastdiv(a.n_kv_head);
   }
   p.lse = a.lse;
   p.lse_stride_h = a.q_seq;
