@@ -126,6 +126,12 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
 
 
+def split_workspace(tnn, q, k, v, causal):
+    """Scratch for the key-split of a half-empty last round, kept across steps (None: the call would not split)."""
+    need = tnn.prefill_workspace_bytes(q, k, v, is_causal=causal)
+    return torch.empty(need, dtype=torch.uint8, device=q.device) if need > 0 else None
+
+
 def shard_of(w, world, rank):
     from tyr_b200 import partition as P
     return P.prefill_shard(w.batch, w.n_kv_head, world, rank)
@@ -336,9 +342,11 @@ def other_workloads(tnn, dev, peaks, par, steps=10, warmup=3):
         (qg, kg, vg), _, sets = prefill_sets(w, sh, dev)
         n = len(sets)
 
-        def step(i, sets=sets, n=n, w=w):
+        ws = split_workspace(tnn, *sets[0][:3], w.causal)
+
+        def step(i, sets=sets, n=n, w=w, ws=ws):
             q, k, v, o, lse = sets[i % n]
-            tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse)
+            tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse, workspace=ws)
         sec = time_events(step, steps, warmup, lambda: None) / steps
         check_rows(par, qg, kg, vg, w.causal, sets[0][3], sets[0][4], 0, 0, 24, w.seed, name)
         out[name] = {"ms": sec * 1e3, "tflops": w.flops / sec / 1e12, "gbs": w.io_bytes / sec / 1e9,
@@ -405,15 +413,18 @@ def sharded_workloads(tnn, dev, rank, world, barrier, all_max, par, steps=10, wa
     (qg, kg, vg), _, sets = prefill_sets(w, sh, dev)
     n = len(sets)
 
+    ws = split_workspace(tnn, *sets[0][:3], w.causal)
+
     def step(i):
         q, k, v, o, lse = sets[i % n]
-        tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse)
+        tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse, workspace=ws)
     sec = all_max(time_events(step, steps, warmup, barrier) / steps)
     check_rows(par, qg, kg, vg, w.causal, sets[0][3], sets[0][4], sh.batch[0], sh.kv_heads[0] * g_, 16,
                w.seed + rank, f"{w.name}@rank{rank}")
     nb, nh = sh.batch[1] - sh.batch[0], sh.kv_heads[1] - sh.kv_heads[0]
     out[w.name] = {"ms": sec * 1e3, "tflops": w.flops / sec / 1e12, "shard_axis": sh.axis,
-                   "shard": f"batch {nb} x kv_heads {nh} per GPU", "buffer_sets": n}
+                   "shard": f"batch {nb} x kv_heads {nh} per GPU", "buffer_sets": n,
+                   "last_round_key_split": ws is not None}
     del sets, qg, kg, vg
 
     w = W.WORKLOADS["qwen3_8b_decode"]
@@ -444,7 +455,8 @@ def run_profile(args):
         w = W.WORKLOADS[args.workload]
         q, k, v = (t.to(dev) for t in W.make_prefill(w))
         o, lse = torch.empty_like(q), torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
-        step = lambda i: tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse)  # noqa: E731
+        ws = split_workspace(tnn, q, k, v, w.causal)
+        step = lambda i: tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse, workspace=ws)  # noqa: E731
         work, unit = w.flops / 1e12, "TFLOP/s"
     elif args.profile == "backward":
         w = W.WORKLOADS[args.workload]
@@ -522,9 +534,11 @@ def run_ours(args):
     (qg, kg, vg), (qh, kh, vh), sets = prefill_sets(w, sh, dev, pin_first=True)
     n_sets = len(sets)
 
+    ws = split_workspace(tnn, *sets[0][:3], w.causal)
+
     def step(i):
         q, k, v, o, lse = sets[i % n_sets]
-        tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse)
+        tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse, workspace=ws)
 
     n0 = tnn.launch_count()
     with ClockSampler(local) as clocks:
@@ -537,7 +551,7 @@ def run_ours(args):
                 step(i)
                 i += 1
             torch.cuda.synchronize()
-    launches = args.steps
+    launches = args.steps * (2 if ws is not None else 1)   # a split launch is the kernel and its merge
     assert tnn.launch_count() - n0 >= args.steps + args.warmup
     if tnn.device_status(local, True) != 0:
         raise RuntimeError("a bounded in-kernel wait gave up during the benchmark")

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 6
+#define TYR_ATTN_ABI_VERSION 7
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -88,9 +88,20 @@ typedef struct TyrAttnPrefillArgs {
                               (cc/src/tyr.cpp:4063-4086).  A query that sees no key at all
                               gets NaN output, as it does from ATen. */
   int64_t key_mask_stride; /* bytes between the mask rows of two batch elements */
+  void* workspace;         /* NULL, or DEVICE scratch of tyr_b200_attn_prefill_workspace_bytes(args)
+                              bytes, 256-byte aligned, private to this call until it has finished on
+                              its stream.  With it a non-causal launch whose last round of work items
+                              fills at most half the SMs computes that round's items as two halves of
+                              their keys and merges them (Tyr/GPU/Kernels/RingAttn.lean:164-180).
+                              Without it, or when it is too small, nothing is split. */
+  int64_t workspace_bytes;
 } TyrAttnPrefillArgs;
 
 int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* args, void* stream);
+/* Bytes of `workspace` with which the call above would split its last round on the current
+ * device; 0 when it would not split (causal, windowed or masked calls, short key sequences, a
+ * last round that is more than half full), negative TYR_ATTN_ERR_* on bad arguments. */
+int64_t tyr_b200_attn_prefill_workspace_bytes(const TyrAttnPrefillArgs* args);
 
 /* Contiguous-layout forms whose argument lists mirror the Lean externs one to
  * one: tensor handles become device pointers, the result tensor becomes the

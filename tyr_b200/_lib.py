@@ -19,7 +19,7 @@ DECODE_STATIC_SCRATCH_BYTES = 16 << 20   # TYR_ATTN_DECODE_STATIC_SCRATCH_BYTES
 
 # every symbol include/tyr_b200_attn.h declares
 EXPORTS = [
-    "tyr_b200_attn_prefill", "tyr_b200_sdpa_4d", "tyr_b200_sdpa_gqa", "tyr_b200_sdpa_gqa_qkv",
+    "tyr_b200_attn_prefill", "tyr_b200_attn_prefill_workspace_bytes", "tyr_b200_sdpa_4d", "tyr_b200_sdpa_gqa", "tyr_b200_sdpa_gqa_qkv",
     "tyr_b200_sdpa_gqa_window", "tyr_b200_sdpa_gqa_mask",
     "tyr_b200_attn_decode_workspace_bytes", "tyr_b200_attn_decode", "tyr_b200_attn_decode_static",
     "tyr_b200_attn_merge", "tyr_b200_attn_qk_prologue",
@@ -39,6 +39,7 @@ class PrefillArgs(ctypes.Structure):
         ("o_stride", c_i64 * 3),
         ("dtype", c_i32), ("is_causal", c_i32), ("scale", c_f32), ("check_mode", c_i32),
         ("window_size", c_i32), ("key_mask", vp), ("key_mask_stride", c_i64),
+        ("workspace", vp), ("workspace_bytes", c_i64),
     ]
 
 
@@ -104,6 +105,8 @@ def load() -> ctypes.CDLL:
     L.tyr_b200_sdpa_gqa_window.restype = ctypes.c_int
     L.tyr_b200_sdpa_gqa_mask.argtypes = [c_u64] * 5 + [vp] * 5 + [c_f64, c_u8, c_u8, vp]
     L.tyr_b200_sdpa_gqa_mask.restype = ctypes.c_int
+    L.tyr_b200_attn_prefill_workspace_bytes.argtypes = [ctypes.POINTER(PrefillArgs)]
+    L.tyr_b200_attn_prefill_workspace_bytes.restype = c_i64
     L.tyr_b200_attn_decode_workspace_bytes.argtypes = [c_i32] * 5
     L.tyr_b200_attn_decode_workspace_bytes.restype = ctypes.c_size_t
     L.tyr_b200_attn_decode.argtypes = [ctypes.POINTER(DecodeArgs), vp]

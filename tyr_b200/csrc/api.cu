@@ -303,6 +303,13 @@ int tyr_b200_attn_backward(const TyrAttnBackwardArgs* a, void* stream) {
                                static_cast<cudaStream_t>(stream));
 }
 
+int64_t tyr_b200_attn_prefill_workspace_bytes(const TyrAttnPrefillArgs* a) {
+  const int rc = check_prefill(a);
+  if (rc) return rc;
+  if (a->dtype != TYR_ATTN_BF16 || a->check_mode) return 0;
+  return tyr::prefill_split_workspace_bytes(*a);
+}
+
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   int rc = check_prefill(a);
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment

@@ -24,6 +24,7 @@ int launch_stalled_wait(long long limit_cycles, int* status, cudaStream_t st);
 
 // prefill_sm100.cu — tcgen05/TMA kernel, bf16, head_dim in {64,128}.
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st);
+long long prefill_split_workspace_bytes(const TyrAttnPrefillArgs& a);  // 0: the launch would not split
 // 128-byte-swizzled 64 x 128 box map over a bf16 [batch, heads, seq, d] tensor with element strides
 // {batch, head, seq}; encoded maps are cached per thread (prefill_sm100.cu).
 int make_tile_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d, const int64_t* stride);

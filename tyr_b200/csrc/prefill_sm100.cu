@@ -95,6 +95,13 @@ struct PrefillParams {
   FastDiv by_chunk_items;     // / (groups_per_chunk * items_per_group)
   FastDiv by_level_full, by_level_last;  // / (groups in the chunk * heads_per_level), full chunks and the last one
   FastDiv by_heads_per_level, by_kv_heads;
+  // Key-split of the last round (prefill_kernel<., ., true> only).  Items split_from .. split_from +
+  // n_split - 1 are each done as two work items over one half of the KV tiles; a half writes a
+  // normalised bf16 partial O [2 halves][n_split][2 tiles][128 rows][D] and its LSE to the
+  // caller's workspace, and prefill_split_merge_kernel combines them.
+  int split_from, n_split;
+  __nv_bfloat16* o_part;
+  float* lse_part;
 };
 
 template <int D>
@@ -150,8 +157,10 @@ struct Item {
   int mblk, b, hkv;
   int hq[2];   // query head of Q tile 0 / 1
   int row[2];  // first query row of Q tile 0 / 1
-  int lo;      // first KV tile of the item (> 0 only under a sliding window)
+  int lo;      // first KV tile of the item (> 0 under a sliding window and for the second half of a split item)
   int n0, n1;  // KV tiles Q tile 0 / Q tile 1 visit, counted from `lo`
+  int part;    // -1, or which half of its keys this work item covers (split items only)
+  int slot;    // split items only: index of the item among the split ones
 };
 // Two ways to fill the two Q-tile slots of an item:
 //  rows  : 256 consecutive rows of one query head (tile 1 sits 128 rows below tile 0);
@@ -230,6 +239,26 @@ __device__ __forceinline__ int snake_item(int it, int total_items, int snake) {
   const long long w = (long long)it * G + c;
   if ((long long)it * G >= total_items) return -1;
   return w < total_items ? (int)w : -2;
+}
+
+// Work item w of the launch: the items before p.split_from as they are, the ones from there on as
+// two halves of their KV tiles each (non-causal launches only, so both Q tiles visit every tile).
+template <int D, bool kWindow, bool kSplit>
+__device__ __forceinline__ Item work_item(int w, const PrefillParams& p) {
+  if (!kSplit || w < p.split_from) {
+    Item it = decode_item<kWindow, D == 64>(w, p);
+    it.part = -1;
+    it.slot = 0;
+    return it;
+  }
+  const int s = w - p.split_from;
+  Item it = decode_item<kWindow, D == 64>(p.split_from + (s >> 1), p);
+  const int half = (it.n1 + 1) >> 1;
+  it.part = s & 1;
+  it.slot = s >> 1;
+  it.lo = it.part ? half : 0;
+  it.n0 = it.n1 = it.part ? it.n1 - half : half;
+  return it;
 }
 
 // The issuing thread shares its SM sub-partition with two softmax warps, so every
@@ -318,11 +347,12 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&sr)[32], uint64_t sl2
 // previous item's epilogue.
 // kWindow compiles the sliding-window and padding-key masks in (rows may then meet tiles in
 // which they see no key); the plain kernel carries none of those checks.
-template <int D, bool kWindow>
+// kSplit compiles the key-split of the last round in (work_item); the plain kernel has no trace of it.
+template <int D, bool kWindow, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               const PrefillParams p) {
+               const PrefillParams p, const __grid_constant__ CUtensorMap tm_op) {
   using C = Cfg<D>;
   using B = Bars<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -336,7 +366,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar = [&](int i) { return sBar + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_items = p.items_per_group * p.n_kv_head * p.batch;
+  // the merge kernel behind a split launch may become resident as SMs fall free (it waits for this grid itself)
+  if (kSplit) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int total_items = p.items_per_group * p.n_kv_head * p.batch + (kSplit ? p.n_split : 0);
 
   if (threadIdx.x == 0) {
     wait_ctl.abort = 0;
@@ -370,7 +402,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow, D == 64>(w, p);
+          const Item im = work_item<D, kWindow, kSplit>(w, p);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (it > 0) ok = ok && mbar_wait(bar(B::q_empty + t), (it - 1) & 1, abortp);
@@ -425,7 +457,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow, D == 64>(w, p);
+          const Item im = work_item<D, kWindow, kSplit>(w, p);
           const int n0 = im.n0, n1 = im.n1;
           ok = mbar_wait(bar(B::q_full + 0), it & 1, abortp) && mbar_wait(bar(B::q_full + 1), it & 1, abortp) &&
                mbar_wait(bar(B::k_full + kc % C::kKStages), (kc / C::kKStages) & 1, abortp);
@@ -516,12 +548,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int it = 0; ok; ++it) {
           const int w = snake_item(it, total_items, p.snake);
           if (w < 0) break;
-          const Item im = decode_item<kWindow, D == 64>(w, p);
+          const Item im = work_item<D, kWindow, kSplit>(w, p);
 #pragma unroll
           for (int t = 0; t < 2; ++t, ++u) {
             ok = mbar_wait(bar(B::o_staged), u & 1, abortp);
             if (!ok) break;
-            if (im.row[t] < p.q_seq) {  // rows past the tensor are clipped by the store; a tile wholly past it is skipped
+            if (kSplit && im.part >= 0) {  // a half's partial tile: all 128 rows, to the workspace
+#pragma unroll
+              for (int kb = 0; kb < C::kBoxes; ++kb)
+                tma_store_4d(&tm_op, sO + kb * C::kBoxBytes, kb * 64, 0, t, im.part * p.n_split + im.slot);
+              tma_store_commit();
+              tma_store_wait_read0();
+            } else if (im.row[t] < p.q_seq) {  // rows past the tensor are clipped by the store; a tile wholly past it is skipped
 #pragma unroll
               for (int kb = 0; kb < C::kBoxes; ++kb)
                 tma_store_4d(&tm_o, sO + kb * C::kBoxBytes, kb * 64, im.row[t], im.hq[t], im.b);
@@ -551,7 +589,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int it = 0; ok; ++it) {
       const int w = snake_item(it, total_items, p.snake);
       if (w < 0) break;
-      const Item im = decode_item<kWindow, D == 64>(w, p);
+      const Item im = work_item<D, kWindow, kSplit>(w, p);
       const int row = (t ? im.row[1] : im.row[0]) + r;  // query index
       const int hq = t ? im.hq[1] : im.hq[0];
       const int n_t = t ? im.n1 : im.n0;
@@ -691,13 +729,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((piece ^ (r & 7)) << 4)),
                          "r"(x), "r"(y), "r"(z), "r"(wq)
                          : "memory");
+          } else if (kSplit && im.part >= 0) {
+            *reinterpret_cast<uint4*>(p.o_part + ((int64_t)((im.part * p.n_split + im.slot) * 2 + t) * kBM + r) * D +
+                                      c * 32 + q4 * 8) = make_uint4(x, y, z, wq);
           } else if (row_ok) {  // straight from registers: 16-byte stores of one row per thread
             *reinterpret_cast<uint4*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s +
                                       c * 32 + q4 * 8) = make_uint4(x, y, z, wq);
           }
         }
       }
-      if (p.lse != nullptr && row_ok)
+      if (kSplit && im.part >= 0)
+        p.lse_part[((im.part * p.n_split + im.slot) * 2 + t) * kBM + r] = 0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
+      else if (p.lse != nullptr && row_ok)
         p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
       // the tile is staged: make the generic-proxy writes visible to the TMA store, then tell the
@@ -809,6 +852,65 @@ int encode_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, i
   return r == CUDA_SUCCESS ? 0 : -TYR_ATTN_ERR_ALIGN;
 }
 
+// Work items of a launch and the key-split of its last round.  A launch runs its items in rounds of
+// one per SM; when the last round is at most half full, a non-causal launch does each of that
+// round's items as two work items over one half of the KV tiles, so the round takes half as long
+// (216 equal items on 148 SMs: 36 + 18 tile steps instead of 36 + 36).  The halves leave normalised
+// partial outputs in the caller's workspace and prefill_split_merge_kernel combines them.
+struct SplitPlan {
+  long long items;  // work items before any split
+  int n_split;      // items of the last round to split (0: none)
+  long long bytes;  // workspace the split needs
+};
+SplitPlan split_plan(const TyrAttnPrefillArgs& a, int n_sm) {
+  SplitPlan sp{0, 0, 0};
+  const int group = a.n_head / a.n_kv_head;
+  const bool masked = a.is_causal || a.window_size > 0;
+  const bool pair = group % 2 == 0 && (masked || a.q_seq <= kBM);
+  const long long n_mblk = pair ? (a.q_seq + kBM - 1) / kBM : (a.q_seq + 2 * kBM - 1) / (2 * kBM);
+  sp.items = n_mblk * (pair ? group / 2 : group) * a.n_kv_head * a.batch;
+  // halves of fewer than 4 KV tiles would not pay for the merge launch
+  if (masked || a.key_mask != nullptr || (a.kv_seq + kBN - 1) / kBN < 8 || a.check_mode) return sp;
+  const long long rem = sp.items % n_sm;
+  if (rem == 0 || 2 * rem > n_sm) return sp;
+  sp.n_split = (int)rem;
+  sp.bytes = rem * 2 * 2 * kBM * ((long long)a.head_dim * 2 + 4);
+  return sp;
+}
+
+// O = w0 O_0 + w1 O_1 with w_i = exp(LSE_i - LSE), LSE = log(exp LSE_0 + exp LSE_1): the merge of
+// Tyr/GPU/Kernels/RingAttn.lean:164-180 over the two halves of a split item.  One warp per query row.
+template <int D>
+__global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillParams p) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int id = blockIdx.x * 8 + warp;  // (slot, tile, row)
+  const int r = id & (kBM - 1), t = (id >> 7) & 1, slot = id >> 8;
+  if (slot >= p.n_split) return;
+  const Item im = decode_item<false, D == 64>(p.split_from + slot, p);
+  const int row = im.row[t] + r;
+  if (row >= p.q_seq) return;
+  const int hq = im.hq[t];
+  const int64_t i0 = ((int64_t)slot * 2 + t) * kBM + r;
+  const int64_t i1 = ((int64_t)(p.n_split + slot) * 2 + t) * kBM + r;
+  const float l0 = p.lse_part[i0], l1 = p.lse_part[i1];
+  const float m = fmaxf(l0, l1);
+  const float e0 = __expf(l0 - m), e1 = __expf(l1 - m);
+  const float inv = 1.0f / (e0 + e1);
+  const float w0 = e0 * inv, w1 = e1 * inv;
+  constexpr int kPer = D / 32;  // columns per lane
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(p.o_part + i0 * D + lane * kPer);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(p.o_part + i1 * D + lane * kPer);
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h +
+                                                         (int64_t)row * p.o_stride_s + lane * kPer);
+#pragma unroll
+  for (int i = 0; i < kPer / 2; ++i) {
+    const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+    po[i] = __floats2bfloat162_rn(w0 * fa.x + w1 * fb.x, w0 * fa.y + w1 * fb.y);
+  }
+  if (lane == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(e0 + e1);
+}
+
 // SMs of the current device (one persistent CTA each)
 int sm_count() {
   int dev = 0, n = 0;
@@ -835,10 +937,15 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -TYR_ATTN_ERR_NO_DEVICE;
     if (!attr_set[dev].load(std::memory_order_acquire)) {
-      cudaError_t attr_err = cudaFuncSetAttribute(prefill_kernel<D, kWindow>,
+      cudaError_t attr_err = cudaFuncSetAttribute(prefill_kernel<D, kWindow, false>,
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)C::kSmemBytes);
       if (attr_err != cudaSuccess) return (int)attr_err;
+      if (!kWindow) {
+        attr_err = cudaFuncSetAttribute(prefill_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)C::kSmemBytes);
+        if (attr_err != cudaSuccess) return (int)attr_err;
+      }
       attr_set[dev].store(true, std::memory_order_release);
     }
   }
@@ -891,8 +998,44 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   p.wait_limit = wait_limit_cycles();
   const long long items = (long long)p.items_per_group * a.n_kv_head * a.batch;
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
+  p.split_from = (int)items;
+  p.n_split = 0;
+  p.o_part = nullptr;
+  p.lse_part = nullptr;
+  if (!kWindow && a.workspace != nullptr) {
+    const SplitPlan sp = split_plan(a, sm_count());
+    if (sp.n_split > 0 && a.workspace_bytes >= sp.bytes && (reinterpret_cast<uintptr_t>(a.workspace) & 255) == 0) {
+      p.n_split = sp.n_split;
+      p.split_from = (int)(items - sp.n_split);
+      p.o_part = static_cast<__nv_bfloat16*>(a.workspace);
+      p.lse_part = reinterpret_cast<float*>(p.o_part + (size_t)sp.n_split * 2 * 2 * kBM * D);
+      CUtensorMap top;
+      const int64_t part_stride[3] = {2ll * kBM * D, (int64_t)kBM * D, D};
+      if ((rc = make_map(&top, p.o_part, 2 * sp.n_split, 2, kBM, D, part_stride))) return rc;
+      const int grid = (int)std::min<long long>(items + sp.n_split, sm_count());
+      prefill_kernel<D, false, true><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, top);
+      count_launch();
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return (int)e;
+      // programmatic stream serialisation: the merge's launch latency hides behind the kernel's tail
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(sp.n_split * 32);
+      cfg.blockDim = dim3(256);
+      cfg.dynamicSmemBytes = 0;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, prefill_split_merge_kernel<D>, p);
+      count_launch();
+      if (e == cudaSuccess) e = cudaGetLastError();
+      return (int)e;
+    }
+  }
   const int grid = (int)std::min<long long>(items, sm_count());
-  prefill_kernel<D, kWindow><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p);
+  prefill_kernel<D, kWindow, false><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, to);
   count_launch();
   return (int)cudaGetLastError();
 }
@@ -901,6 +1044,11 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
 
 int make_tile_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, int d, const int64_t* stride) {
   return make_map(m, ptr, batch, heads, seq, d, stride);
+}
+
+long long prefill_split_workspace_bytes(const TyrAttnPrefillArgs& a) {
+  if (a.head_dim != 64 && a.head_dim != 128) return 0;
+  return split_plan(a, sm_count()).bytes;
 }
 
 int launch_prefill_sm100(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t st) {

@@ -70,7 +70,8 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                  lse: Optional[torch.Tensor] = None, return_lse: bool = True,
                  check_mode: bool = False, window_size: int = 0,
-                 key_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                 key_mask: Optional[torch.Tensor] = None,
+                 workspace=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """O = softmax(Q K^T * scale + causal) V and the per-row LSE.
 
     q [B,Hq,Sq,D]; k, v [B,Hkv,Skv,D] (Hq % Hkv == 0, query head h reads KV head
@@ -83,6 +84,9 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     from every query, the key side of lean_torch_sdpa_gqa_mask (cc/src/tyr.cpp:4063-4086).
     Launcher convention of Examples/GPU/RunFlashAttn.lean:68-81: outputs may be
     pre-allocated by the caller and are written in place.
+    `workspace`: a caller-kept uint8 CUDA tensor of `prefill_workspace_bytes(...)` bytes for the
+    key-split of a half-empty last round; when the call would split, one is allocated if none is given
+    (`workspace=False`: never split).
     """
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -101,9 +105,25 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
                 or key_mask.stride(1) != 1 or tuple(key_mask.shape) != (k.shape[0], k.shape[2])):
             raise ValueError("key_mask must be a uint8/bool CUDA tensor [batch, kv_seq]")
     a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode, window_size, key_mask)
+    L = _lib.load()
     with torch.cuda.device(q.device):
-        check(_lib.load().tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
+        need = 0 if workspace is False else int(L.tyr_b200_attn_prefill_workspace_bytes(ctypes.byref(a)))
+        if need > 0:
+            if workspace is None:
+                workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+            if (workspace.dtype != torch.uint8 or not workspace.is_contiguous() or workspace.device != q.device
+                    or workspace.data_ptr() % 256 != 0):
+                raise ValueError("workspace must be a contiguous uint8 CUDA tensor on q's device, 256-byte aligned")
+            a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+        check(L.tyr_b200_attn_prefill(ctypes.byref(a), _stream_ptr(q)))
     return out, lse
+
+
+def prefill_workspace_bytes(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = True) -> int:
+    """Bytes of `workspace` with which `attentionFwd` on these tensors would split its last round (0: it would not)."""
+    a = _fill_prefill(q, k, v, q, None, is_causal, None, False)  # only shapes and strides are looked at
+    with torch.cuda.device(q.device):
+        return max(int(_lib.load().tyr_b200_attn_prefill_workspace_bytes(ctypes.byref(a))), 0)
 
 
 def attentionBwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
