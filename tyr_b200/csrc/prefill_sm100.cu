@@ -887,7 +887,7 @@ __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillP
   const int id = blockIdx.x * 8 + warp;  // (slot, tile, row)
   const int r = id & (kBM - 1), t = (id >> 7) & 1, slot = id >> 8;
   if (slot >= p.n_split) return;
-  const Item im = decode_item<false, D == 64>(p.split_from + slot, p);
+  const Item im = decode_item<false, true>(p.split_from + slot, p);
   const int row = im.row[t] + r;
   if (row >= p.q_seq) return;
   const int hq = im.hq[t];
