@@ -452,12 +452,14 @@ def run_profile(args):
     from tyr_b200 import nn as tnn
     dev = torch.device("cuda", 0)
     if args.profile == "prefill":
+        from tyr_b200 import partition as P
         w = W.WORKLOADS[args.workload]
-        q, k, v = (t.to(dev) for t in W.make_prefill(w))
+        r_, n_ = (int(x) for x in args.shard_of.split("/")) if args.shard_of else (0, 1)   # one shard of an N-way cut
+        q, k, v = (t.contiguous().to(dev) for t in P.slice_prefill(*W.make_prefill(w), P.prefill_shard(w.batch, w.n_kv_head, n_, r_)))
         o, lse = torch.empty_like(q), torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
         ws = split_workspace(tnn, q, k, v, w.causal)
         step = lambda i: tnn.attentionFwd(q, k, v, is_causal=w.causal, out=o, lse=lse, workspace=ws)  # noqa: E731
-        work, unit = w.flops / 1e12, "TFLOP/s"
+        work, unit = w.flops / n_ / 1e12, "TFLOP/s"
     elif args.profile == "backward":
         w = W.WORKLOADS[args.workload]
         q, k, v = (t.to(dev) for t in W.make_prefill(w))

@@ -18,9 +18,15 @@
 //                         into tensor memory, P^T and dS^T go back to tensor memory as bf16 and feed
 //                         dV += P^T dO, dK += dS^T Q as the A operand, the streamed tile read MN-major
 //                         as B.  dK and dV accumulate in tensor memory over the whole group: no
-//                         atomics, a deterministic sum.  Tensor memory (512 columns): S^T [0,128)
-//                         dP^T [128,256) dK [256,256+D) dV [256+D,256+2D); bf16 P^T / dS^T overwrite the
-//                         first 64 columns of S^T / dP^T once those are in registers.
+//                         atomics, a deterministic sum.  Tensor memory (512 columns): two score regions
+//                         [0,128) and [128,256), dK [256,256+D), dV [256+D,256+2D).  The regions swap
+//                         roles with every streamed pair: S^T of pair g sits in region g & 1 and, once
+//                         in registers, leaves it to the bf16 overlays (P^T on its first 64 columns,
+//                         dS^T on its last 64); dP^T of pair g sits in the other region, which takes
+//                         S^T of pair g + 1 as soon as dP^T is in registers.  A step is therefore two
+//                         halves: P^T from S^T alone, formed while the tensor pipe still works on the
+//                         previous pair's dK and this pair's dP^T, then dS^T from P and dP^T.  Issue
+//                         order per pair: dV(g), S^T(g+1), dK(g), dP^T(g+1).
 //   bwd_dq_kernel<D>    : persistent; one work unit = 128 query rows of a (batch, query head).  Q and
 //                         dO stay, K and V stream; S = Q K^T, dP = dO V^T, dQ += dS K, with dS in two
 //                         buffers of its own so that the next score products run while dS is formed.
@@ -60,15 +66,18 @@ struct BCfg {
   static constexpr int res_full = 0;                   // resident pair landed
   static constexpr int str_full = 1;                   // [2] streamed pair landed
   static constexpr int str_empty = 3;                  // [2] accumulating products have read the pair
-  static constexpr int s_full = 5;                     // S and dP in tensor memory
-  static constexpr int p_full = 6;                     // P / dS written (one arrival per elementwise warp)
+  static constexpr int s_full = 5;                     // S^T in tensor memory
+  static constexpr int p_full = 6;                     // P^T written (one arrival per elementwise warp)
   static constexpr int acc_full = 7;                   // last accumulating product done
   static constexpr int pair = 8;                       // [4] per lane quarter: both warps hold their score columns
                                                        //     in registers (P / dS overwrite each other's columns)
   static constexpr int res_empty = 12;                 // the unit's last score products have read K and V
   static constexpr int acc_free = 13;                  // the epilogue has read dK and dV (8 warp arrivals)
-  static constexpr int p_half = 14;                    // P / dS of score columns 0..63 written (8 warp arrivals)
-  static constexpr int kNumBars = 15;
+  static constexpr int ds_half = 14;                   // dS^T of score columns 0..63 written (8 warp arrivals)
+  static constexpr int ds_full = 15;                   // dS^T of score columns 64..127 written (8 warp arrivals)
+  static constexpr int dp_full = 16;                   // dP^T in tensor memory
+  static constexpr int dp_taken = 17;                  // dP^T is in registers: its columns are free (8 warp arrivals)
+  static constexpr int kNumBars = 18;
   static constexpr uint32_t kSmemBytes = kBarOff + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kTmemS = 0, kTmemDP = 128, kTmemAcc1 = 256, kTmemAcc2 = 256 + D;
@@ -188,7 +197,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     wait_ctl.abort = 0;
     wait_ctl.limit = p.wait_limit;
     for (int i = 0; i < C::kNumBars; ++i)
-      mbar_init(bar(i), (i == C::p_full || i == C::p_half || i == C::acc_free) ? 8u
+      mbar_init(bar(i), (i == C::p_full || i == C::ds_half || i == C::ds_full || i == C::dp_taken || i == C::acc_free) ? 8u
                         : (i >= C::pair && i < C::pair + 4) ? 2u : 1u);
     mbar_fence_init();
     tma_prefetch_desc(&tm_k);
@@ -252,18 +261,26 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     // the whole warp runs the loop, convergent; one elected lane issues the MMAs and commits
     {
       const uint32_t issue = elect_one();
-      const uint32_t tS = tmem + C::kTmemS, tDP = tmem + C::kTmemDP;
       const uint32_t tA1 = tmem + C::kTmemAcc1, tA2 = tmem + C::kTmemAcc2;
       const uint32_t res1_lo = umma_desc_lo(base + C::kRes1, 16), res2_lo = umma_desc_lo(base + C::kRes2, 16);
-      auto scores = [&](int g) {  // S^T = K Q^T, dP^T = V dO^T for streamed pair number g
+      // The two 128-column score regions swap roles from one streamed pair to the next: pair g has
+      // S^T in region g & 1 and dP^T in the other.  Once S^T is in registers its region takes the two
+      // bf16 overlays, P^T on its first 64 columns and dS^T on its last 64; the dP^T region is free as
+      // soon as dP^T is in registers and takes S^T of pair g + 1, and when the accumulating products
+      // of pair g have read the overlays their region takes dP^T of pair g + 1.
+      auto region = [&](int g, int which) { return tmem + (((g + which) & 1) ? C::kTmemDP : C::kTmemS); };
+      auto score_s = [&](int g) {   // S^T = K Q^T of pair g
         const int s = g % C::kStages;
-        const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
         if (!mbar_wait(bar(C::str_full + s), (g / C::kStages) & 1, abortp)) return false;
         tc_fence_after();
-        issue_nt<D>(issue, tS, res1_lo, umma_desc_lo(t1, 16));
-        issue_nt<D>(issue, tDP, res2_lo, umma_desc_lo(t1 + C::kTileBytes, 16));
+        issue_nt<D>(issue, region(g, 0), res1_lo, umma_desc_lo(base + C::kStr + s * 2 * C::kTileBytes, 16));
         umma_commit_p(bar(C::s_full), issue);
         return true;
+      };
+      auto score_dp = [&](int g) {  // dP^T = V dO^T of pair g (its tiles have landed: S^T of the pair came first)
+        const int s = g % C::kStages;
+        issue_nt<D>(issue, region(g, 1), res2_lo, umma_desc_lo(base + C::kStr + s * 2 * C::kTileBytes + C::kTileBytes, 16));
+        umma_commit_p(bar(C::dp_full), issue);
       };
       bool ok = true;
       int it = 0, rc = 0;
@@ -273,33 +290,46 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const KvUnit w = kv_unit(u, p);
         if (w.n_iter == 0) continue;
         ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
-        if (ok) ok = scores(it);
+        if (ok) ok = score_s(it);
+        if (ok) score_dp(it);
         if (ok && w.n_iter == 1) umma_commit_p(bar(C::res_empty), issue);
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           const int s = it % C::kStages;
           const uint32_t t1 = base + C::kStr + s * 2 * C::kTileBytes;
-          // the first 64 query columns of P^T / dS^T are written while the second 64 are still
-          // being formed: their share of the accumulating products starts now
-          ok = mbar_wait(bar(C::p_half), it & 1, abortp);
+          const uint32_t tP = region(it, 0), tDS = tP + 64;
+          const uint32_t q_mn = umma_desc_lo(t1, C::kBoxBytes), do_mn = umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes);
+          // dV += P^T dO as soon as P^T is written (it is formed from S^T alone, ahead of dS^T)
+          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
           // the unit's first accumulating products overwrite dK / dV: the previous unit's
           // epilogue must have read them
           if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t q_mn = umma_desc_lo(t1, C::kBoxBytes), do_mn = umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes);
-          issue_acc<D>(issue, tA1, tDP, q_mn, i > 0, 0);   // dK += dS^T Q
-          issue_acc<D>(issue, tA2, tS, do_mn, i > 0, 0);   // dV += P^T dO
-          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
+          issue_acc<D>(issue, tA2, tP, do_mn, i > 0);
+          // S^T of the next pair into the region dP^T has left
+          if (i + 1 < w.n_iter) {
+            ok = mbar_wait(bar(C::dp_taken), it & 1, abortp);
+            if (!ok) break;
+            tc_fence_after();
+            ok = score_s(it + 1);
+            if (!ok) break;
+          }
+          // dK += dS^T Q, the first 64 query columns while the second 64 are still being formed
+          ok = mbar_wait(bar(C::ds_half), it & 1, abortp);
           if (!ok) break;
           tc_fence_after();
-          issue_acc<D>(issue, tA1, tDP, q_mn, true, 1);
-          issue_acc<D>(issue, tA2, tS, do_mn, true, 1);
+          issue_acc<D>(issue, tA1, tDS, q_mn, i > 0, 0);
+          ok = mbar_wait(bar(C::ds_full), it & 1, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc<D>(issue, tA1, tDS, q_mn, true, 1);
           umma_commit_p(bar(C::str_empty + s), issue);
           if (i + 1 < w.n_iter) {
-            ok = scores(it + 1);
+            // dP^T of the next pair into the region whose overlays the products above have read
+            score_dp(it + 1);
             // K and V are read by the score products only: after the unit's last pair of them
             // the producer may fetch the next unit's
-            if (ok && i + 2 == w.n_iter) umma_commit_p(bar(C::res_empty), issue);
+            if (i + 2 == w.n_iter) umma_commit_p(bar(C::res_empty), issue);
           } else {
             umma_commit_p(bar(C::acc_full), issue);
           }
@@ -313,7 +343,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     const int half = (warp - 4) >> 2;   // query columns [64 half, 64 half + 64), output columns likewise
     const int r = quarter * 32 + lane;  // key row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t tS = tmem + lane_addr + C::kTmemS, tDP = tmem + lane_addr + C::kTmemDP;
     const uint64_t sl2x2 = pack_f32x2(p.sl2, p.sl2), scale2 = pack_f32x2(p.scale, p.scale);
     bool ok = true;
     int it = 0, rc = 0;
@@ -323,6 +352,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       const KvUnit w = kv_unit(u, p);
       const int row0 = w.blk * kT;
       for (int i = 0; i < w.n_iter; ++i, ++it) {
+        // the score regions swap roles with every streamed pair (see the MMA issuer)
+        const uint32_t tS = tmem + lane_addr + ((it & 1) ? C::kTmemDP : C::kTmemS);
+        const uint32_t tDP = tmem + lane_addr + ((it & 1) ? C::kTmemS : C::kTmemDP);
         ok = mbar_wait(bar(C::s_full), it & 1, abortp);
         // the query columns' statistics landed with the streamed tiles: observe that barrier
         // directly (it completed before the products this warp was woken by were issued)
@@ -342,50 +374,41 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const float* nl_col = reinterpret_cast<const float*>(smem_raw + (base - raw) + C::kStatOff +
                                                              (it % C::kStages) * C::kStatBytes);
         const float* nd_col = nl_col + kT;
-        // This warp's two 32-column chunks of S^T and dP^T go to registers first: chunk `half` of the
-        // first 64 query columns and chunk 2 + `half` of the second 64.  bf16 P^T / dS^T of chunk c
-        // land on columns [16 c, 16 c + 16) of S^T / dP^T, i.e. on chunks 0 and 1, which belong to
-        // different warps of the pair: the two meet once both hold their columns in registers.
-        uint32_t sr2[2][32], dp2[2][32];
+        // First half of the step, from S^T alone: P^T.  This warp's two 32-column chunks of S^T go to
+        // registers: chunk `half` of the first 64 query columns and chunk 2 + `half` of the second
+        // 64.  bf16 P^T of chunk c lands on columns [16 c, 16 c + 16) of the region, i.e. on chunks 0
+        // and 1, which belong to different warps of the pair: the two meet once both hold their
+        // columns in registers.  P stays in registers as fp32 for dS.
+        uint32_t pr2[2][32];
 #pragma unroll
-        for (int step = 0; step < 2; ++step) {
-          tmem_ld32(tS + (2 * step + half) * 32, sr2[step]);
-          tmem_ld32(tDP + (2 * step + half) * 32, dp2[step]);
-        }
+        for (int step = 0; step < 2; ++step) tmem_ld32(tS + (2 * step + half) * 32, pr2[step]);
         tmem_wait_ld();
 #pragma unroll
-        for (int step = 0; step < 2; ++step) {
-          tmem_ld_ready(sr2[step]);
-          tmem_ld_ready(dp2[step]);
-        }
+        for (int step = 0; step < 2; ++step) tmem_ld_ready(pr2[step]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::pair + quarter));
 #pragma unroll
         for (int step = 0; step < 2; ++step) {
           const int c = 2 * step + half;
-          uint32_t(&sr)[32] = sr2[step];
-          uint32_t(&dp)[32] = dp2[step];
+          uint32_t(&sr)[32] = pr2[step];
           if (masked) {
 #pragma unroll
             for (int x = 0; x < 32; ++x)
               if (c * 32 + x < c_first || c * 32 + x >= c_limit) sr[x] = 0xff800000u;  // -inf: P = 0
           }
-          uint32_t pk_p[16], pk_s[16];
+          uint32_t pk_p[16];
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
             // statistics of the two query columns (every lane reads the same addresses)
             const float2 a = *reinterpret_cast<const float2*>(nl_col + c * 32 + 2 * x);
-            const float2 d = *reinterpret_cast<const float2*>(nd_col + c * 32 + 2 * x);
             const uint64_t t2 = fma_f32x2(pack_u32x2(sr[2 * x], sr[2 * x + 1]), sl2x2, pack_f32x2(a.x, a.y));
             float t0, t1;
             unpack_f32x2(t2, t0, t1);
             const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
-            const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, pack_f32x2(d.x, d.y));
-            float d0, d1;
-            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u2), d0, d1);
+            sr[2 * x] = __float_as_uint(p0);
+            sr[2 * x + 1] = __float_as_uint(p1);
             pk_p[x] = pack_bf16x2(p0, p1);
-            pk_s[x] = pack_bf16x2(d0, d1);
           }
           if (step == 0) {
             ok = mbar_wait(bar(C::pair + quarter), it & 1, abortp);
@@ -394,13 +417,49 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
             tc_fence_after();
           }
           tmem_st16(tS + c * 16, pk_p);
-          tmem_st16(tDP + c * 16, pk_s);
+        }
+        if (!ok) break;
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::p_full));
+
+        // Second half, once dP^T has arrived: dS^T = P (scale dP - scale delta), written behind P^T on
+        // the last 64 columns of the same region (they held the second 64 query columns of S^T, in
+        // registers since the pair met).  The region dP^T leaves takes the next pair's S^T.
+        ok = mbar_wait(bar(C::dp_full), it & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t dp2[2][32];
+#pragma unroll
+        for (int step = 0; step < 2; ++step) tmem_ld32(tDP + (2 * step + half) * 32, dp2[step]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int step = 0; step < 2; ++step) tmem_ld_ready(dp2[step]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::dp_taken));
+#pragma unroll
+        for (int step = 0; step < 2; ++step) {
+          const int c = 2 * step + half;
+          uint32_t(&pr)[32] = pr2[step];
+          uint32_t(&dp)[32] = dp2[step];
+          uint32_t pk_s[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const float2 d = *reinterpret_cast<const float2*>(nd_col + c * 32 + 2 * x);
+            const uint64_t u2 = fma_f32x2(pack_u32x2(dp[2 * x], dp[2 * x + 1]), scale2, pack_f32x2(d.x, d.y));
+            float d0, d1;
+            unpack_f32x2(mul_f32x2(pack_u32x2(pr[2 * x], pr[2 * x + 1]), u2), d0, d1);
+            pk_s[x] = pack_bf16x2(d0, d1);
+          }
+          tmem_st16(tS + 64 + c * 16, pk_s);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(step == 0 ? C::p_half : C::p_full));
+          if (lane == 0) mbar_arrive(bar(step == 0 ? C::ds_half : C::ds_full));
         }
-        if (!ok) break;
       }
       if (!ok) break;
 

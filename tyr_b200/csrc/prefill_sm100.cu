@@ -159,8 +159,7 @@ struct Item {
   int row[2];  // first query row of Q tile 0 / 1
   int lo;      // first KV tile of the item (> 0 under a sliding window and for the second half of a split item)
   int n0, n1;  // KV tiles Q tile 0 / Q tile 1 visit, counted from `lo`
-  int part;    // -1, or which half of its keys this work item covers (split items only)
-  int slot;    // split items only: index of the item among the split ones
+  int part_slot;  // -1, or (half of the keys this work item covers) * n_split + index among the split items
 };
 // Two ways to fill the two Q-tile slots of an item:
 //  rows  : 256 consecutive rows of one query head (tile 1 sits 128 rows below tile 0);
@@ -247,17 +246,16 @@ template <int D, bool kWindow, bool kSplit>
 __device__ __forceinline__ Item work_item(int w, const PrefillParams& p) {
   if (!kSplit || w < p.split_from) {
     Item it = decode_item<kWindow, D == 64>(w, p);
-    it.part = -1;
-    it.slot = 0;
+    it.part_slot = -1;
     return it;
   }
   const int s = w - p.split_from;
   Item it = decode_item<kWindow, D == 64>(p.split_from + (s >> 1), p);
   const int half = (it.n1 + 1) >> 1;
-  it.part = s & 1;
-  it.slot = s >> 1;
-  it.lo = it.part ? half : 0;
-  it.n0 = it.n1 = it.part ? it.n1 - half : half;
+  const int part = s & 1;
+  it.part_slot = part * p.n_split + (s >> 1);
+  it.lo = part ? half : 0;
+  it.n0 = it.n1 = part ? it.n1 - half : half;
   return it;
 }
 
@@ -553,10 +551,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int t = 0; t < 2; ++t, ++u) {
             ok = mbar_wait(bar(B::o_staged), u & 1, abortp);
             if (!ok) break;
-            if (kSplit && im.part >= 0) {  // a half's partial tile: all 128 rows, to the workspace
+            if (kSplit && im.part_slot >= 0) {  // a half's partial tile: all 128 rows, to the workspace
 #pragma unroll
               for (int kb = 0; kb < C::kBoxes; ++kb)
-                tma_store_4d(&tm_op, sO + kb * C::kBoxBytes, kb * 64, 0, t, im.part * p.n_split + im.slot);
+                tma_store_4d(&tm_op, sO + kb * C::kBoxBytes, kb * 64, 0, t, im.part_slot);
               tma_store_commit();
               tma_store_wait_read0();
             } else if (im.row[t] < p.q_seq) {  // rows past the tensor are clipped by the store; a tile wholly past it is skipped
@@ -729,8 +727,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((piece ^ (r & 7)) << 4)),
                          "r"(x), "r"(y), "r"(z), "r"(wq)
                          : "memory");
-          } else if (kSplit && im.part >= 0) {
-            *reinterpret_cast<uint4*>(p.o_part + ((int64_t)((im.part * p.n_split + im.slot) * 2 + t) * kBM + r) * D +
+          } else if (kSplit && im.part_slot >= 0) {
+            *reinterpret_cast<uint4*>(p.o_part + ((int64_t)(im.part_slot * 2 + t) * kBM + r) * D +
                                       c * 32 + q4 * 8) = make_uint4(x, y, z, wq);
           } else if (row_ok) {  // straight from registers: 16-byte stores of one row per thread
             *reinterpret_cast<uint4*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s +
@@ -738,8 +736,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-      if (kSplit && im.part >= 0)
-        p.lse_part[((im.part * p.n_split + im.slot) * 2 + t) * kBM + r] = 0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
+      if (kSplit && im.part_slot >= 0)
+        p.lse_part[(im.part_slot * 2 + t) * kBM + r] = 0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
       else if (p.lse != nullptr && row_ok)
         p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] =
             0.6931471805599453f * (m_ref * sl2 + lg2_approx(l));
