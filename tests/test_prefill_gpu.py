@@ -322,6 +322,22 @@ def test_full_size_workloads_by_sampled_rows_and_properties(name):
     assert ((lc - lse[b:b + 1, hk * g:(hk + 1) * g]).abs() / lc.abs().clamp(min=1)).max().item() <= LSE_REL
 
 
+def test_tabled_schedule_gives_the_static_schedule_bits():
+    # A causal launch whose K/V exceed the L2 budget (items in several chunks) deals its items to the
+    # CTAs by a host-built table; the same (batch, KV head) groups computed alone run the static
+    # schedule.  An item's arithmetic does not depend on who runs it or when: identical bits.
+    w = W.WORKLOADS["qwen3_8b_prefill"]
+    q, k, v = (t.to(DEV) for t in W.make_prefill(w))
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=True)
+    o_again, lse_again = tnn.attentionFwd(q, k, v, is_causal=True)      # the table is cached now
+    assert torch.equal(o, o_again) and torch.equal(lse, lse_again)
+    g = w.n_head // w.n_kv_head
+    for b, hk in ((0, 0), (w.batch - 1, w.n_kv_head - 1), (1, 3)):
+        os_, ls_ = tnn.attentionFwd(q[b:b + 1, hk * g:(hk + 1) * g], k[b:b + 1, hk:hk + 1], v[b:b + 1, hk:hk + 1],
+                                    is_causal=True)
+        assert torch.equal(os_, o[b:b + 1, hk * g:(hk + 1) * g]) and torch.equal(ls_, lse[b:b + 1, hk * g:(hk + 1) * g])
+
+
 def test_merge_entry_point_against_oracle_and_full_attention():
     q, k, v = randn(1, 2, 64, 128, seed=61), randn(1, 2, 600, 128, seed=62), randn(1, 2, 600, 128, seed=63)
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
