@@ -338,6 +338,27 @@ def test_tabled_schedule_gives_the_static_schedule_bits():
         assert torch.equal(os_, o[b:b + 1, hk * g:(hk + 1) * g]) and torch.equal(ls_, lse[b:b + 1, hk * g:(hk + 1) * g])
 
 
+def test_graph_capture_of_a_call_that_would_build_a_table():
+    # a new launch geometry met for the first time on a capturing stream: no table is built (that
+    # would allocate and copy synchronously), the static schedule is captured, and the replay gives
+    # the bits of the eager call that follows (which does build the table)
+    q, k, v = (randn(3, 8, 8192, 128, seed=s).to(DEV) for s in (11, 12, 13))
+    o, lse = torch.empty_like(q), torch.empty(q.shape[:3], device=DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            tnn.attentionFwd(q, k, v, is_causal=True, out=o, lse=lse)
+    torch.cuda.current_stream().wait_stream(side)
+    o.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    o_eager, lse_eager = tnn.attentionFwd(q, k, v, is_causal=True)
+    assert torch.equal(o, o_eager) and torch.equal(lse, lse_eager)
+    _sampled_rows_vs_oracle(q, k, v, o, lse, True, n=16, seed=3)
+
+
 def test_merge_entry_point_against_oracle_and_full_attention():
     q, k, v = randn(1, 2, 64, 128, seed=61), randn(1, 2, 600, 128, seed=62), randn(1, 2, 600, 128, seed=63)
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
