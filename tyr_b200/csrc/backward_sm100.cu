@@ -225,7 +225,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (u < 0) continue;
         const KvUnit w = kv_unit(u, p);
         if (w.n_iter == 0) continue;
-        if (rc > 0) ok = mbar_wait(bar(C::res_empty), (rc - 1) & 1, abortp);
+        if (rc > 0) ok = mbar_wait_q(bar(C::res_empty), (rc - 1) & 1, abortp);
         if (!ok) break;
         mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
 #pragma unroll
@@ -235,7 +235,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         }
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           const int s = it % C::kStages;
-          if (it >= C::kStages) ok = mbar_wait(bar(C::str_empty + s), ((it / C::kStages) - 1) & 1, abortp);
+          if (it >= C::kStages) ok = mbar_wait_q(bar(C::str_empty + s), ((it / C::kStages) - 1) & 1, abortp);
           if (!ok) break;
           const int hq = w.head * p.group + i / w.per_head, qblk = w.lo + i % w.per_head;
           const uint32_t dst = base + C::kStr + s * 2 * C::kTileBytes;
@@ -271,7 +271,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       auto region = [&](int g, int which) { return tmem + (((g + which) & 1) ? C::kTmemDP : C::kTmemS); };
       auto score_s = [&](int g) {   // S^T = K Q^T of pair g
         const int s = g % C::kStages;
-        if (!mbar_wait(bar(C::str_full + s), (g / C::kStages) & 1, abortp)) return false;
+        if (!mbar_wait_q(bar(C::str_full + s), (g / C::kStages) & 1, abortp)) return false;
         tc_fence_after();
         issue_nt<D>(issue, region(g, 0), res1_lo, umma_desc_lo(base + C::kStr + s * 2 * C::kTileBytes, 16));
         umma_commit_p(bar(C::s_full), issue);
@@ -289,7 +289,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         if (u < 0) continue;
         const KvUnit w = kv_unit(u, p);
         if (w.n_iter == 0) continue;
-        ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
+        ok = mbar_wait_q(bar(C::res_full), rc & 1, abortp);
         if (ok) ok = score_s(it);
         if (ok) score_dp(it);
         if (ok && w.n_iter == 1) umma_commit_p(bar(C::res_empty), issue);
@@ -299,27 +299,27 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
           const uint32_t tP = region(it, 0), tDS = tP + 64;
           const uint32_t q_mn = umma_desc_lo(t1, C::kBoxBytes), do_mn = umma_desc_lo(t1 + C::kTileBytes, C::kBoxBytes);
           // dV += P^T dO as soon as P^T is written (it is formed from S^T alone, ahead of dS^T)
-          ok = mbar_wait(bar(C::p_full), it & 1, abortp);
+          ok = mbar_wait_q(bar(C::p_full), it & 1, abortp);
           // the unit's first accumulating products overwrite dK / dV: the previous unit's
           // epilogue must have read them
-          if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
+          if (ok && i == 0 && rc > 0) ok = mbar_wait_q(bar(C::acc_free), (rc - 1) & 1, abortp);
           if (!ok) break;
           tc_fence_after();
           issue_acc<D>(issue, tA2, tP, do_mn, i > 0);
           // S^T of the next pair into the region dP^T has left
           if (i + 1 < w.n_iter) {
-            ok = mbar_wait(bar(C::dp_taken), it & 1, abortp);
+            ok = mbar_wait_q(bar(C::dp_taken), it & 1, abortp);
             if (!ok) break;
             tc_fence_after();
             ok = score_s(it + 1);
             if (!ok) break;
           }
           // dK += dS^T Q, the first 64 query columns while the second 64 are still being formed
-          ok = mbar_wait(bar(C::ds_half), it & 1, abortp);
+          ok = mbar_wait_q(bar(C::ds_half), it & 1, abortp);
           if (!ok) break;
           tc_fence_after();
           issue_acc<D>(issue, tA1, tDS, q_mn, i > 0, 0);
-          ok = mbar_wait(bar(C::ds_full), it & 1, abortp);
+          ok = mbar_wait_q(bar(C::ds_full), it & 1, abortp);
           if (!ok) break;
           tc_fence_after();
           issue_acc<D>(issue, tA1, tDS, q_mn, true, 1);
@@ -355,10 +355,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         // the score regions swap roles with every streamed pair (see the MMA issuer)
         const uint32_t tS = tmem + lane_addr + ((it & 1) ? C::kTmemDP : C::kTmemS);
         const uint32_t tDP = tmem + lane_addr + ((it & 1) ? C::kTmemS : C::kTmemDP);
-        ok = mbar_wait(bar(C::s_full), it & 1, abortp);
+        ok = mbar_wait_q(bar(C::s_full), it & 1, abortp);
         // the query columns' statistics landed with the streamed tiles: observe that barrier
         // directly (it completed before the products this warp was woken by were issued)
-        if (ok) ok = mbar_wait(bar(C::str_full + it % C::kStages), (it / C::kStages) & 1, abortp);
+        if (ok) ok = mbar_wait_q(bar(C::str_full + it % C::kStages), (it / C::kStages) & 1, abortp);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -411,7 +411,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
             pk_p[x] = pack_bf16x2(p0, p1);
           }
           if (step == 0) {
-            ok = mbar_wait(bar(C::pair + quarter), it & 1, abortp);
+            ok = mbar_wait_q(bar(C::pair + quarter), it & 1, abortp);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -427,7 +427,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         // Second half, once dP^T has arrived: dS^T = P (scale dP - scale delta), written behind P^T on
         // the last 64 columns of the same region (they held the second 64 query columns of S^T, in
         // registers since the pair met).  The region dP^T leaves takes the next pair's S^T.
-        ok = mbar_wait(bar(C::dp_full), it & 1, abortp);
+        ok = mbar_wait_q(bar(C::dp_full), it & 1, abortp);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -466,7 +466,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
       // epilogue: dK and dV -> bf16 -> global, one key row per thread, half of the columns per warp
       // of the pair; keys that no query sees get zeros without touching tensor memory
       if (w.n_iter > 0) {
-        ok = mbar_wait(bar(C::acc_full), rc & 1, abortp);
+        ok = mbar_wait_q(bar(C::acc_full), rc & 1, abortp);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -635,7 +635,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (u < 0) break;  // only the last round can be short
         const QUnit w = q_unit(u, p);
         const int hkv = w.head / p.group;
-        if (rc > 0) ok = mbar_wait(bar(C::res_empty), (rc - 1) & 1, abortp);
+        if (rc > 0) ok = mbar_wait_q(bar(C::res_empty), (rc - 1) & 1, abortp);
         if (!ok) break;
         mbar_expect_tx(bar(C::res_full), 2 * C::kTileBytes);
 #pragma unroll
@@ -645,14 +645,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           const int ks = it % C::kKStages, vs = it % C::kVStages;
-          if (it >= C::kKStages) ok = mbar_wait(bar(C::k_empty + ks), ((it / C::kKStages) - 1) & 1, abortp);
+          if (it >= C::kKStages) ok = mbar_wait_q(bar(C::k_empty + ks), ((it / C::kKStages) - 1) & 1, abortp);
           if (!ok) break;
           mbar_expect_tx(bar(C::k_full + ks), C::kTileBytes);
 #pragma unroll
           for (int kb = 0; kb < C::kBoxes; ++kb)
             tma_load_4d(base + C::kK + ks * C::kTileBytes + kb * C::kBoxBytes, &tm_k, bar(C::k_full + ks), kb * 64,
                         (w.lo + i) * kT, hkv, w.b);
-          if (it >= C::kVStages) ok = mbar_wait(bar(C::v_empty + vs), ((it / C::kVStages) - 1) & 1, abortp);
+          if (it >= C::kVStages) ok = mbar_wait_q(bar(C::v_empty + vs), ((it / C::kVStages) - 1) & 1, abortp);
           if (!ok) break;
           mbar_expect_tx(bar(C::v_full + vs), C::kTileBytes);
 #pragma unroll
@@ -671,8 +671,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const uint32_t q_lo = umma_desc_lo(base + C::kQ, 16), do_lo = umma_desc_lo(base + C::kDO, 16);
       auto scores = [&](int g) {  // S = Q K^T, dP = dO V^T for streamed pair number g; V is free afterwards
         const int ks = g % C::kKStages, vs = g % C::kVStages;
-        if (!mbar_wait(bar(C::k_full + ks), (g / C::kKStages) & 1, abortp)) return false;
-        if (!mbar_wait(bar(C::v_full + vs), (g / C::kVStages) & 1, abortp)) return false;
+        if (!mbar_wait_q(bar(C::k_full + ks), (g / C::kKStages) & 1, abortp)) return false;
+        if (!mbar_wait_q(bar(C::v_full + vs), (g / C::kVStages) & 1, abortp)) return false;
         tc_fence_after();
         issue_nt<D>(issue, tS, q_lo, umma_desc_lo(base + C::kK + ks * C::kTileBytes, 16));
         issue_nt<D>(issue, tDP, do_lo, umma_desc_lo(base + C::kV + vs * C::kTileBytes, 16));
@@ -686,22 +686,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int u = unit_of_round(round, n_units);
         if (u < 0) break;  // only the last round can be short
         const QUnit w = q_unit(u, p);
-        ok = mbar_wait(bar(C::res_full), rc & 1, abortp);
+        ok = mbar_wait_q(bar(C::res_full), rc & 1, abortp);
         // S and dP of the previous unit's last pair must be in the elementwise warps' registers
-        if (ok && it > 0) ok = mbar_wait(bar(C::sdp_free), (it - 1) & 1, abortp);
+        if (ok && it > 0) ok = mbar_wait_q(bar(C::sdp_free), (it - 1) & 1, abortp);
         if (ok) ok = scores(it);
         if (ok && w.n_iter == 1) umma_commit_p(bar(C::res_empty), issue);
         for (int i = 0; i < w.n_iter && ok; ++i, ++it) {
           if (i + 1 < w.n_iter) {
             // S(i) and dP(i) are in the elementwise warps' registers: the next pair may overwrite them
-            ok = mbar_wait(bar(C::sdp_free), it & 1, abortp);
+            ok = mbar_wait_q(bar(C::sdp_free), it & 1, abortp);
             if (ok) ok = scores(it + 1);
             if (!ok) break;
             if (i + 2 == w.n_iter) umma_commit_p(bar(C::res_empty), issue);  // Q and dO are read by score products only
           }
-          ok = mbar_wait(bar(C::p_full + (it & 1)), (it >> 1) & 1, abortp);
+          ok = mbar_wait_q(bar(C::p_full + (it & 1)), (it >> 1) & 1, abortp);
           // the unit's first dQ product overwrites the accumulator the previous epilogue reads
-          if (ok && i == 0 && rc > 0) ok = mbar_wait(bar(C::acc_free), (rc - 1) & 1, abortp);
+          if (ok && i == 0 && rc > 0) ok = mbar_wait_q(bar(C::acc_free), (rc - 1) & 1, abortp);
           if (!ok) break;
           tc_fence_after();
           const int ks = it % C::kKStages;
@@ -731,7 +731,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const float nl_row = p.neg_lse2[at], nd_row = p.neg_delta_s[at];
       const uint64_t nl2 = pack_f32x2(nl_row, nl_row), nd2 = pack_f32x2(nd_row, nd_row);
       for (int i = 0; i < w.n_iter; ++i, ++it) {
-        ok = mbar_wait(bar(C::s_full), it & 1, abortp);
+        ok = mbar_wait_q(bar(C::s_full), it & 1, abortp);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -802,7 +802,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
 
       // epilogue: dQ -> bf16 -> global, one row per thread, half of the columns per warp of the pair
-      ok = mbar_wait(bar(C::acc_full), rc & 1, abortp);
+      ok = mbar_wait_q(bar(C::acc_full), rc & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
