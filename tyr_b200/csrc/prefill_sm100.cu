@@ -939,6 +939,7 @@ int sm_count() {
 // schedule).  Building one allocates and copies synchronously, so a launch that is being captured
 // into a graph does not build (it uses a table that exists, else the static schedule).
 constexpr int kMaxItemTables = 16;
+constexpr long long kMaxTabledItems = 1ll << 18;  // 1 MB of table, some 10 ms to build
 struct ItemTable {
   int dev, grid, batch, n_kv_head, n_mblk, pair_heads, items_per_group, groups_per_chunk, causal, kv_seq;
   int* table;
@@ -1132,7 +1133,9 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   // Items of unequal length in several L2-sized chunks and many rounds: deal them to the CTAs by a
   // table (item_of_table).  Equal items gain nothing from it, and the tabled instantiation measured
   // 2.6 % slower than the plain one on them (Flux-shaped: 1128 vs 1158 TFLOP/s), so they stay static.
-  if (!kWindow && D == 128 && p.causal && !p.snake && items >= 4ll * grid && item_table_for(p, grid, st)) {
+  // (and not for launches so large that the table itself would weigh: 4 bytes and a heap step per item)
+  if (!kWindow && D == 128 && p.causal && !p.snake && items >= 4ll * grid && items <= kMaxTabledItems &&
+      item_table_for(p, grid, st)) {
     prefill_kernel<128, false, false, true><<<grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tq, tk, tv, to, p, to);
     count_launch();
     return (int)cudaGetLastError();
