@@ -107,7 +107,9 @@ def attentionFwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: b
     a = _fill_prefill(q, k, v, out, lse, is_causal, scale, check_mode, window_size, key_mask)
     L = _lib.load()
     with torch.cuda.device(q.device):
-        need = 0 if workspace is False else int(L.tyr_b200_attn_prefill_workspace_bytes(ctypes.byref(a)))
+        # only unmasked, non-causal calls are ever split: no query for the others
+        may_split = workspace is not False and not is_causal and window_size == 0 and key_mask is None and not check_mode
+        need = int(L.tyr_b200_attn_prefill_workspace_bytes(ctypes.byref(a))) if may_split else 0
         if need > 0:
             if workspace is None:
                 workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
