@@ -33,7 +33,7 @@ def test_abi_version_and_error_strings(built_lib):
 
 
 def test_struct_sizes_match_the_c_layout():
-    # 5 pointers, 6 int32, 12 int64, int32 int32 float int32 int32 (+4 padding), pointer, int64
+    # 5 pointers, 6 int32, 12 int64, int32 int32 float int32 int32 (+4 padding), pointer, int64, pointer, int64
     assert ctypes.sizeof(_lib.PrefillArgs) == 5 * 8 + 6 * 4 + 12 * 8 + 5 * 4 + 4 + 8 + 8 + 8 + 8
     assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
     # 10 pointers, uint64, 6 int32, 24 int64, int32 int32 float int32, pointer, int64
