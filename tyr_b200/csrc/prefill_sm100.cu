@@ -891,12 +891,15 @@ SplitPlan split_plan(const TyrAttnPrefillArgs& a, int n_sm) {
 }
 
 // O = w0 O_0 + w1 O_1 with w_i = exp(LSE_i - LSE), LSE = log(exp LSE_0 + exp LSE_1): the merge of
-// Tyr/GPU/Kernels/RingAttn.lean:164-180 over the two halves of a split item.  One warp per query row.
+// Tyr/GPU/Kernels/RingAttn.lean:164-180 over the two halves of a split item.  16 bytes of a row per lane.
 template <int D>
 __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int kLanesPerRow = D / 8;            // 16 bytes of a row per lane
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int id = blockIdx.x * 8 + warp;  // (slot, tile, row)
+  const int id = (blockIdx.x * 8 + warp) * kRowsPerWarp + lane / kLanesPerRow;  // (slot, tile, row)
+  const int col = (lane % kLanesPerRow) * 8;
   const int r = id & (kBM - 1), t = (id >> 7) & 1, slot = id >> 8;
   if (slot >= p.n_split) return;
   const Item im = decode_item<false, true>(p.split_from + slot, p);
@@ -910,17 +913,19 @@ __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillP
   const float e0 = __expf(l0 - m), e1 = __expf(l1 - m);
   const float inv = 1.0f / (e0 + e1);
   const float w0 = e0 * inv, w1 = e1 * inv;
-  constexpr int kPer = D / 32;  // columns per lane
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(p.o_part + i0 * D + lane * kPer);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(p.o_part + i1 * D + lane * kPer);
-  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h +
-                                                         (int64_t)row * p.o_stride_s + lane * kPer);
+  const uint4 va = *reinterpret_cast<const uint4*>(p.o_part + i0 * D + col);
+  const uint4 vb = *reinterpret_cast<const uint4*>(p.o_part + i1 * D + col);
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&va);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+  uint4 vo;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&vo);
 #pragma unroll
-  for (int i = 0; i < kPer / 2; ++i) {
+  for (int i = 0; i < 4; ++i) {
     const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
     po[i] = __floats2bfloat162_rn(w0 * fa.x + w1 * fb.x, w0 * fa.y + w1 * fb.y);
   }
-  if (lane == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(e0 + e1);
+  *reinterpret_cast<uint4*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s + col) = vo;
+  if (col == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(e0 + e1);
 }
 
 // SMs of the current device (one persistent CTA each)
@@ -1114,7 +1119,7 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
       if (e != cudaSuccess) return (int)e;
       // programmatic stream serialisation: the merge's launch latency hides behind the kernel's tail
       cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(sp.n_split * 32);
+      cfg.gridDim = dim3(sp.n_split * 256 / (8 * (32 / (D / 8))));   // 256 rows per item, 8 warps of 32 / (D / 8) rows
       cfg.blockDim = dim3(256);
       cfg.dynamicSmemBytes = 0;
       cfg.stream = st;
