@@ -217,6 +217,54 @@ extern "C" lean_object* lean_launch_tyrB200AttnFwd(b_lean_obj_arg q_, b_lean_obj
   }
 }
 
+// The same launcher with the caller's scratch for the key-split of a half-empty last round
+// (`workspace`: uint8 CUDA tensor, 256-byte aligned; one with no elements means none), and the
+// size query the caller sizes that tensor with (0: this call would not split).
+extern "C" lean_object* lean_launch_tyrB200AttnFwdWs(b_lean_obj_arg q_, b_lean_obj_arg k_, b_lean_obj_arg v_,
+                                                     b_lean_obj_arg o_, b_lean_obj_arg lse_,
+                                                     b_lean_obj_arg workspace_, uint8_t is_causal,
+                                                     uint64_t stream, lean_object* /*w*/) {
+  try {
+    auto q = borrowTensor(q_), k = borrowTensor(k_), v = borrowTensor(v_), o = borrowTensor(o_),
+         lse = borrowTensor(lse_), ws = borrowTensor(workspace_);
+    for (const auto* t : {&q, &k, &v, &o}) {
+      if (!t->is_cuda()) return io_error("tyrB200AttnFwdWs: tensors must be CUDA tensors");
+      if (t->dim() != 4) return io_error("tyrB200AttnFwdWs: tensors must be [batch, heads, seq, head_dim]");
+      if (t->scalar_type() != at::kBFloat16) return io_error("tyrB200AttnFwdWs: tensors must be bfloat16");
+      if (t->stride(3) != 1) return io_error("tyrB200AttnFwdWs: head_dim must have unit stride");
+    }
+    if (!lse.is_cuda() || !lse.is_contiguous() || lse.scalar_type() != at::kFloat ||
+        lse.numel() != q.size(0) * q.size(1) * q.size(2))
+      return io_error("tyrB200AttnFwdWs: lse must be a contiguous float32 [batch, n_head, seq] CUDA tensor");
+    if (ws.numel() > 0 && (!ws.is_cuda() || !ws.is_contiguous() || ws.element_size() != 1))
+      return io_error("tyrB200AttnFwdWs: workspace must be a contiguous one-byte-per-element CUDA tensor");
+    TyrAttnPrefillArgs a;
+    fill_args(a, q, k, v, o, lse.data_ptr<float>(), is_causal != 0);
+    if (ws.numel() > 0) {
+      a.workspace = ws.data_ptr();
+      a.workspace_bytes = static_cast<int64_t>(ws.numel());
+    }
+    int rc = tyr_b200_attn_prefill(&a, reinterpret_cast<void*>(stream));
+    if (rc != 0) return io_error(tyr_b200_attn_strerror(rc));
+    return lean_io_result_mk_ok(lean_box(0));
+  } catch (const std::exception& e) {
+    return io_error(e.what());
+  }
+}
+extern "C" uint64_t lean_tyrB200AttnFwdWorkspaceBytes(b_lean_obj_arg q_, b_lean_obj_arg k_, b_lean_obj_arg v_,
+                                                      uint8_t is_causal) {
+  try {
+    auto q = borrowTensor(q_), k = borrowTensor(k_), v = borrowTensor(v_);
+    if (!q.is_cuda() || q.dim() != 4 || k.dim() != 4 || v.dim() != 4 || q.scalar_type() != at::kBFloat16) return 0;
+    TyrAttnPrefillArgs a;
+    fill_args(a, q, k, v, q, nullptr, is_causal != 0);  // only shapes and strides are looked at
+    const int64_t n = tyr_b200_attn_prefill_workspace_bytes(&a);
+    return n > 0 ? static_cast<uint64_t>(n) : 0;
+  } catch (const std::exception&) {
+    return 0;
+  }
+}
+
 // Decode over Tyr's dense KVCache ([batch, n_kv_head, maxLen, head_dim],
 // Tyr/Model/Qwen/Attention.lean:54-68) with the cache's shared `seq` counter as kv_len.
 extern "C" lean_object* lean_launch_tyrB200AttnDecode(b_lean_obj_arg q_, b_lean_obj_arg kcache_,

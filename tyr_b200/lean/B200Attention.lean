@@ -19,6 +19,17 @@ open torch
 opaque tyrB200AttnFwd.launch
     (q k v out lse : @& Tensor) (isCausal : UInt8) (stream : Tyr.GPU.CudaStream) : IO Unit
 
+/-- `tyrB200AttnFwd` with the caller's scratch for the key-split of a half-empty last round of work
+    items (non-causal calls; `workspace`: uint8 CUDA tensor of `tyrB200AttnFwd.workspaceBytes` bytes,
+    one with no elements for none).  C side: `lean_launch_tyrB200AttnFwdWs`. -/
+@[extern "lean_launch_tyrB200AttnFwdWs"]
+opaque tyrB200AttnFwdWs.launch
+    (q k v out lse workspace : @& Tensor) (isCausal : UInt8) (stream : Tyr.GPU.CudaStream) : IO Unit
+
+/-- Bytes of scratch with which the call above would split its last round (0: it would not). -/
+@[extern "lean_tyrB200AttnFwdWorkspaceBytes"]
+opaque tyrB200AttnFwd.workspaceBytes (q k v : @& Tensor) (isCausal : UInt8) : UInt64
+
 /-- Single-token decode over the dense KV cache with the cache's `seq` counter as `kvLen`.
     C side: `lean_launch_tyrB200AttnDecode`. -/
 @[extern "lean_launch_tyrB200AttnDecode"]
