@@ -17,6 +17,9 @@ the run exits non-zero on a miss.
 
 Besides the contract keys the line carries the other workloads kernel-only under
 "other_workloads" (N = 1) or "strong_scaling_sharded" (N > 1), decode as KV GB/s.
+
+`--shard-of R/N` runs rank R's shard of the N-GPU job alone on one GPU, without a
+process group: the shard's time and its oracle parity where N GPUs are not to be had.
 """
 from __future__ import annotations
 
