@@ -45,6 +45,25 @@ def test_single_round_is_split_and_matches_the_oracle(D, Sq, Skv):
     _close_to_unsplit(qd, kd, vd, o, lse)
 
 
+@pytest.mark.parametrize("B,H,parts", [(1, 8, 4), (2, 20, 3), (4, 16, 2)])
+def test_three_and_four_parts(B, H, parts):
+    # few items against many SMs: 8 items -> 4 parts each, 40 -> 3, 64 -> 2 (on 148 SMs)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    items = B * H
+    if min(sms // items, 4) != parts:
+        pytest.skip("this device's SM count gives another number of parts")
+    q, k, v = (randn(B, H, 256, 128, seed=3 + H).to(DEV), randn(B, H, 2304, 128, seed=4 + H).to(DEV),
+               randn(B, H, 2304, 128, seed=5 + H).to(DEV))
+    need = tnn.prefill_workspace_bytes(q, k, v, is_causal=False)
+    assert need == items * parts * 2 * 128 * (128 * 2 + 4)
+    o, lse = tnn.attentionFwd(q, k, v, is_causal=False)
+    _close_to_unsplit(q, k, v, o, lse)
+    ro, rlse = c_oracle.sdpa(q[:1, :2].float().cpu().numpy(), k[:1, :2].float().cpu().numpy(),
+                             v[:1, :2].float().cpu().numpy(), False)
+    assert np.abs(o[:1, :2].float().cpu().numpy() - ro).max() <= O_MAX_ABS
+    assert (np.abs(lse[:1, :2].cpu().numpy() - rlse) / np.maximum(np.abs(rlse), 1.0)).max() <= LSE_REL
+
+
 def test_last_of_two_rounds_is_split():
     # 12 heads x 14 row blocks of 256 = 168 items on 148 SMs: 20 items in the second round
     sms = torch.cuda.get_device_properties(0).multi_processor_count
@@ -53,7 +72,8 @@ def test_last_of_two_rounds_is_split():
     rem = 168 % sms
     if rem == 0 or 2 * rem > sms:
         pytest.skip("this device's SM count leaves no half-empty round for 168 items")
-    assert need == rem * 2 * 2 * 128 * (128 * 2 + 4)
+    parts = min(sms // rem, 4, 28 // 4)   # as many parts as fit the SMs, at least four KV tiles each
+    assert need == rem * parts * 2 * 128 * (128 * 2 + 4)
     o, lse = tnn.attentionFwd(q, k, v, is_causal=False)
     _close_to_unsplit(q, k, v, o, lse)
     # exact rows of the split items (the lowest row blocks come last in the item order) and of others

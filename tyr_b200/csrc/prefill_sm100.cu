@@ -98,8 +98,8 @@ struct PrefillParams {
   FastDiv by_level_full, by_level_last;  // / (groups in the chunk * heads_per_level), full chunks and the last one
   FastDiv by_heads_per_level, by_kv_heads;
   // Key-split of the last round (prefill_kernel<., ., true> only).  Items split_from .. split_from +
-  // n_split - 1 are each done as two work items over one half of the KV tiles; a half writes a
-  // normalised bf16 partial O [2 halves][n_split][2 tiles][128 rows][D] and its LSE to the
+  // n_split - 1 are each done as n_parts (2 to 4) work items over one part of the KV tiles; a part
+  // writes a normalised bf16 partial O [n_parts][n_split][2 tiles][128 rows][D] and its LSE to the
   // caller's workspace, and prefill_split_merge_kernel combines them.
   int split_from, n_split;
   __nv_bfloat16* o_part;
@@ -108,6 +108,9 @@ struct PrefillParams {
   // item the CTA works on in that round, -1 once it has none left.
   const int* item_table;
   int table_rounds;
+  // (key-split, continued: kept behind the fields above so that their offsets stay what they were)
+  int n_parts;
+  FastDiv by_parts;
 };
 
 template <int D>
@@ -165,7 +168,7 @@ struct Item {
   int row[2];  // first query row of Q tile 0 / 1
   int lo;      // first KV tile of the item (> 0 under a sliding window and for the second half of a split item)
   int n0, n1;  // KV tiles Q tile 0 / Q tile 1 visit, counted from `lo`
-  int part_slot;  // -1, or (half of the keys this work item covers) * n_split + index among the split items
+  int part_slot;  // -1, or (part of the keys this work item covers) * n_split + index among the split items
 };
 // Two ways to fill the two Q-tile slots of an item:
 //  rows  : 256 consecutive rows of one query head (tile 1 sits 128 rows below tile 0);
@@ -255,7 +258,7 @@ __device__ __forceinline__ int item_of_table(int it, const PrefillParams& p) {
 }
 
 // Work item w of the launch: the items before p.split_from as they are, the ones from there on as
-// two halves of their KV tiles each (non-causal launches only, so both Q tiles visit every tile).
+// two to four parts of their KV tiles each (non-causal launches only, so both Q tiles visit every tile).
 template <int D, bool kWindow, bool kSplit>
 __device__ __forceinline__ Item work_item(int w, const PrefillParams& p) {
   if (!kSplit || w < p.split_from) {
@@ -264,12 +267,13 @@ __device__ __forceinline__ Item work_item(int w, const PrefillParams& p) {
     return it;
   }
   const int s = w - p.split_from;
-  Item it = decode_item<kWindow, D == 64>(p.split_from + (s >> 1), p);
-  const int half = (it.n1 + 1) >> 1;
-  const int part = s & 1;
-  it.part_slot = part * p.n_split + (s >> 1);
-  it.lo = part ? half : 0;
-  it.n0 = it.n1 = part ? it.n1 - half : half;
+  const int slot = p.by_parts.div(s);
+  const int part = s - slot * p.n_parts;
+  Item it = decode_item<kWindow, D == 64>(p.split_from + slot, p);
+  const int n = it.n1;  // KV tiles of the whole item; part k covers tiles [k n / parts, (k + 1) n / parts)
+  it.part_slot = part * p.n_split + slot;
+  it.lo = part * n / p.n_parts;
+  it.n0 = it.n1 = (part + 1) * n / p.n_parts - it.lo;
   return it;
 }
 
@@ -380,7 +384,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the merge kernel behind a split launch may become resident as SMs fall free (it waits for this grid itself)
   if (kSplit) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int total_items = p.items_per_group * p.n_kv_head * p.batch + (kSplit ? p.n_split : 0);
+  const int total_items = p.items_per_group * p.n_kv_head * p.batch + (kSplit ? p.n_split * (p.n_parts - 1) : 0);
 
   if (threadIdx.x == 0) {
     wait_ctl.abort = 0;
@@ -866,32 +870,36 @@ int encode_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, i
 
 // Work items of a launch and the key-split of its last round.  A launch runs its items in rounds of
 // one per SM; when the last round is at most half full, a non-causal launch does each of that
-// round's items as two work items over one half of the KV tiles, so the round takes half as long
-// (216 equal items on 148 SMs: 36 + 18 tile steps instead of 36 + 36).  The halves leave normalised
+// round's items as two to four work items over one part of the KV tiles each (as many parts as fit
+// the SMs, at least four KV tiles per part), so the round takes a half to a quarter as long (216
+// equal items on 148 SMs: 36 + 18 tile steps instead of 36 + 36).  The parts leave normalised
 // partial outputs in the caller's workspace and prefill_split_merge_kernel combines them.
 struct SplitPlan {
   long long items;  // work items before any split
   int n_split;      // items of the last round to split (0: none)
+  int n_parts;      // parts each of them is done in (2 to 4)
   long long bytes;  // workspace the split needs
 };
 SplitPlan split_plan(const TyrAttnPrefillArgs& a, int n_sm) {
-  SplitPlan sp{0, 0, 0};
+  SplitPlan sp{0, 0, 0, 0};
   const int group = a.n_head / a.n_kv_head;
   const bool masked = a.is_causal || a.window_size > 0;
   const bool pair = group % 2 == 0 && (masked || a.q_seq <= kBM);
   const long long n_mblk = pair ? (a.q_seq + kBM - 1) / kBM : (a.q_seq + 2 * kBM - 1) / (2 * kBM);
   sp.items = n_mblk * (pair ? group / 2 : group) * a.n_kv_head * a.batch;
-  // halves of fewer than 4 KV tiles would not pay for the merge launch
-  if (masked || a.key_mask != nullptr || (a.kv_seq + kBN - 1) / kBN < 8 || a.check_mode) return sp;
+  // parts of fewer than 4 KV tiles would not pay for the merge launch
+  const int nkv = (a.kv_seq + kBN - 1) / kBN;
+  if (masked || a.key_mask != nullptr || nkv < 8 || a.check_mode) return sp;
   const long long rem = sp.items % n_sm;
   if (rem == 0 || 2 * rem > n_sm) return sp;
   sp.n_split = (int)rem;
-  sp.bytes = rem * 2 * 2 * kBM * ((long long)a.head_dim * 2 + 4);
+  sp.n_parts = (int)std::min<long long>(std::min<long long>(n_sm / rem, 4), nkv / 4);
+  sp.bytes = rem * sp.n_parts * 2 * kBM * ((long long)a.head_dim * 2 + 4);
   return sp;
 }
 
-// O = w0 O_0 + w1 O_1 with w_i = exp(LSE_i - LSE), LSE = log(exp LSE_0 + exp LSE_1): the merge of
-// Tyr/GPU/Kernels/RingAttn.lean:164-180 over the two halves of a split item.  16 bytes of a row per lane.
+// O = sum_i w_i O_i with w_i = exp(LSE_i - LSE), LSE = log sum_i exp LSE_i: the merge of
+// Tyr/GPU/Kernels/RingAttn.lean:164-180 over the parts of a split item.  16 bytes of a row per lane.
 template <int D>
 __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -907,25 +915,29 @@ __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillP
   if (row >= p.q_seq) return;
   const int hq = im.hq[t];
   const int64_t i0 = ((int64_t)slot * 2 + t) * kBM + r;
-  const int64_t i1 = ((int64_t)(p.n_split + slot) * 2 + t) * kBM + r;
-  const float l0 = p.lse_part[i0], l1 = p.lse_part[i1];
-  const float m = fmaxf(l0, l1);
-  const float e0 = __expf(l0 - m), e1 = __expf(l1 - m);
-  const float inv = 1.0f / (e0 + e1);
-  const float w0 = e0 * inv, w1 = e1 * inv;
-  const uint4 va = *reinterpret_cast<const uint4*>(p.o_part + i0 * D + col);
-  const uint4 vb = *reinterpret_cast<const uint4*>(p.o_part + i1 * D + col);
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&va);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+  const int64_t part_stride = (int64_t)p.n_split * 2 * kBM;  // rows between two parts of one item
+  float m = -INFINITY;
+  for (int k = 0; k < p.n_parts; ++k) m = fmaxf(m, p.lse_part[i0 + k * part_stride]);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+  for (int k = 0; k < p.n_parts; ++k) {
+    const float wk = __expf(p.lse_part[i0 + k * part_stride] - m);
+    wsum += wk;
+    const uint4 vk = *reinterpret_cast<const uint4*>(p.o_part + (i0 + k * part_stride) * D + col);
+    const __nv_bfloat162* pk = reinterpret_cast<const __nv_bfloat162*>(&vk);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(pk[i]);
+      acc[2 * i] = fmaf(wk, f.x, acc[2 * i]);
+      acc[2 * i + 1] = fmaf(wk, f.y, acc[2 * i + 1]);
+    }
+  }
+  const float inv = 1.0f / wsum;
   uint4 vo;
   __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&vo);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
-    po[i] = __floats2bfloat162_rn(w0 * fa.x + w1 * fb.x, w0 * fa.y + w1 * fb.y);
-  }
+  for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
   *reinterpret_cast<uint4*>(p.o + im.b * p.o_stride_b + hq * p.o_stride_h + (int64_t)row * p.o_stride_s + col) = vo;
-  if (col == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(e0 + e1);
+  if (col == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(wsum);
 }
 
 // SMs of the current device (one persistent CTA each)
@@ -1098,6 +1110,8 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
   if (items > 0x7fffffffLL) return -TYR_ATTN_ERR_TOO_LARGE;
   p.split_from = (int)items;
   p.n_split = 0;
+  p.n_parts = 1;
+  p.by_parts = make_fastdiv(1);
   p.o_part = nullptr;
   p.lse_part = nullptr;
   p.item_table = nullptr;
@@ -1106,13 +1120,15 @@ int launch(const TyrAttnPrefillArgs& a, float scale, int* status, cudaStream_t s
     const SplitPlan sp = split_plan(a, sm_count());
     if (sp.n_split > 0 && a.workspace_bytes >= sp.bytes && (reinterpret_cast<uintptr_t>(a.workspace) & 255) == 0) {
       p.n_split = sp.n_split;
+      p.n_parts = sp.n_parts;
+      p.by_parts = make_fastdiv(sp.n_parts);
       p.split_from = (int)(items - sp.n_split);
       p.o_part = static_cast<__nv_bfloat16*>(a.workspace);
-      p.lse_part = reinterpret_cast<float*>(p.o_part + (size_t)sp.n_split * 2 * 2 * kBM * D);
+      p.lse_part = reinterpret_cast<float*>(p.o_part + (size_t)sp.n_split * sp.n_parts * 2 * kBM * D);
       CUtensorMap top;
       const int64_t part_stride[3] = {2ll * kBM * D, (int64_t)kBM * D, D};
-      if ((rc = make_map(&top, p.o_part, 2 * sp.n_split, 2, kBM, D, part_stride))) return rc;
-      const int grid = (int)std::min<long long>(items + sp.n_split, sm_count());
+      if ((rc = make_map(&top, p.o_part, sp.n_parts * sp.n_split, 2, kBM, D, part_stride))) return rc;
+      const int grid = (int)std::min<long long>(items + (long long)sp.n_split * (sp.n_parts - 1), sm_count());
       prefill_kernel<D, false, true, false><<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, top);
       count_launch();
       cudaError_t e = cudaGetLastError();
