@@ -91,7 +91,7 @@ typedef struct TyrAttnPrefillArgs {
   void* workspace;         /* NULL, or DEVICE scratch of tyr_b200_attn_prefill_workspace_bytes(args)
                               bytes, 256-byte aligned, private to this call until it has finished on
                               its stream.  With it a non-causal launch whose last round of work items
-                              fills at most half the SMs computes that round's items in two to four
+                              fills at most half the SMs computes that round's items in two to eight
                               parts of their keys and merges them (Tyr/GPU/Kernels/RingAttn.lean:164-180).
                               Without it, or when it is too small, nothing is split. */
   int64_t workspace_bytes;

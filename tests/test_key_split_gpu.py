@@ -45,15 +45,16 @@ def test_single_round_is_split_and_matches_the_oracle(D, Sq, Skv):
     _close_to_unsplit(qd, kd, vd, o, lse)
 
 
-@pytest.mark.parametrize("B,H,parts", [(1, 8, 4), (2, 20, 3), (4, 16, 2)])
-def test_three_and_four_parts(B, H, parts):
-    # few items against many SMs: 8 items -> 4 parts each, 40 -> 3, 64 -> 2 (on 148 SMs)
+@pytest.mark.parametrize("B,H,Skv,parts", [(1, 8, 2304, 4), (2, 20, 2304, 3), (4, 16, 2304, 2), (1, 8, 4200, 8), (1, 24, 4096, 6)])
+def test_more_than_two_parts(B, H, Skv, parts):
+    # few items against many SMs (148): 8 items of 18 KV tiles -> 4 parts each, 40 -> 3, 64 -> 2,
+    # 8 items of 33 tiles -> 8, 24 items -> 6
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     items = B * H
-    if min(sms // items, 4) != parts:
+    if min(sms // items, 8, ((Skv + 127) // 128) // 4) != parts:
         pytest.skip("this device's SM count gives another number of parts")
-    q, k, v = (randn(B, H, 256, 128, seed=3 + H).to(DEV), randn(B, H, 2304, 128, seed=4 + H).to(DEV),
-               randn(B, H, 2304, 128, seed=5 + H).to(DEV))
+    q, k, v = (randn(B, H, 256, 128, seed=3 + H).to(DEV), randn(B, H, Skv, 128, seed=4 + H).to(DEV),
+               randn(B, H, Skv, 128, seed=5 + H).to(DEV))
     need = tnn.prefill_workspace_bytes(q, k, v, is_causal=False)
     assert need == items * parts * 2 * 128 * (128 * 2 + 4)
     o, lse = tnn.attentionFwd(q, k, v, is_causal=False)
@@ -72,7 +73,7 @@ def test_last_of_two_rounds_is_split():
     rem = 168 % sms
     if rem == 0 or 2 * rem > sms:
         pytest.skip("this device's SM count leaves no half-empty round for 168 items")
-    parts = min(sms // rem, 4, 28 // 4)   # as many parts as fit the SMs, at least four KV tiles each
+    parts = min(sms // rem, 8, 28 // 4)   # as many parts as fit the SMs, at least four KV tiles each
     assert need == rem * parts * 2 * 128 * (128 * 2 + 4)
     o, lse = tnn.attentionFwd(q, k, v, is_causal=False)
     _close_to_unsplit(q, k, v, o, lse)

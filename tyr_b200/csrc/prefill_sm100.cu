@@ -98,7 +98,7 @@ struct PrefillParams {
   FastDiv by_level_full, by_level_last;  // / (groups in the chunk * heads_per_level), full chunks and the last one
   FastDiv by_heads_per_level, by_kv_heads;
   // Key-split of the last round (prefill_kernel<., ., true> only).  Items split_from .. split_from +
-  // n_split - 1 are each done as n_parts (2 to 4) work items over one part of the KV tiles; a part
+  // n_split - 1 are each done as n_parts (2 to 8) work items over one part of the KV tiles; a part
   // writes a normalised bf16 partial O [n_parts][n_split][2 tiles][128 rows][D] and its LSE to the
   // caller's workspace, and prefill_split_merge_kernel combines them.
   int split_from, n_split;
@@ -258,7 +258,7 @@ __device__ __forceinline__ int item_of_table(int it, const PrefillParams& p) {
 }
 
 // Work item w of the launch: the items before p.split_from as they are, the ones from there on as
-// two to four parts of their KV tiles each (non-causal launches only, so both Q tiles visit every tile).
+// two to eight parts of their KV tiles each (non-causal launches only, so both Q tiles visit every tile).
 template <int D, bool kWindow, bool kSplit>
 __device__ __forceinline__ Item work_item(int w, const PrefillParams& p) {
   if (!kSplit || w < p.split_from) {
@@ -870,14 +870,15 @@ int encode_map(CUtensorMap* m, const void* ptr, int batch, int heads, int seq, i
 
 // Work items of a launch and the key-split of its last round.  A launch runs its items in rounds of
 // one per SM; when the last round is at most half full, a non-causal launch does each of that
-// round's items as two to four work items over one part of the KV tiles each (as many parts as fit
-// the SMs, at least four KV tiles per part), so the round takes a half to a quarter as long (216
+// round's items as two to eight work items over one part of the KV tiles each (as many parts as fit
+// the SMs, at least four KV tiles per part), so the round takes a half to an eighth as long (216
 // equal items on 148 SMs: 36 + 18 tile steps instead of 36 + 36).  The parts leave normalised
 // partial outputs in the caller's workspace and prefill_split_merge_kernel combines them.
+constexpr int kMaxSplitParts = 8;
 struct SplitPlan {
   long long items;  // work items before any split
   int n_split;      // items of the last round to split (0: none)
-  int n_parts;      // parts each of them is done in (2 to 4)
+  int n_parts;      // parts each of them is done in (2 to 8)
   long long bytes;  // workspace the split needs
 };
 SplitPlan split_plan(const TyrAttnPrefillArgs& a, int n_sm) {
@@ -893,7 +894,7 @@ SplitPlan split_plan(const TyrAttnPrefillArgs& a, int n_sm) {
   const long long rem = sp.items % n_sm;
   if (rem == 0 || 2 * rem > n_sm) return sp;
   sp.n_split = (int)rem;
-  sp.n_parts = (int)std::min<long long>(std::min<long long>(n_sm / rem, 4), nkv / 4);
+  sp.n_parts = (int)std::min<long long>(std::min<long long>(n_sm / rem, kMaxSplitParts), nkv / 4);
   sp.bytes = rem * sp.n_parts * 2 * kBM * ((long long)a.head_dim * 2 + 4);
   return sp;
 }
