@@ -945,10 +945,10 @@ __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillP
 int sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  static int cache[64] = {0};
-  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  static std::atomic<int> cache[64] = {};
+  if (dev >= 0 && dev < 64 && (n = cache[dev].load(std::memory_order_relaxed)) > 0) return n;
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  if (dev >= 0 && dev < 64) cache[dev] = n;
+  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
   return n;
 }
 
