@@ -35,7 +35,7 @@ extern "C" {
 
 /* argument errors (returned negated: -TYR_ATTN_ERR_x) */
 #define TYR_ATTN_ERR_NULL 1        /* a required pointer is NULL */
-#define TYR_ATTN_ERR_SHAPE 2       /* a size is zero/negative or n_head % n_kv_head != 0 */
+#define TYR_ATTN_ERR_SHAPE 2       /* a size is negative (or zero where zero has no meaning) or n_head % n_kv_head != 0 */
 #define TYR_ATTN_ERR_HEAD_DIM 3    /* head_dim not in {64,128} (tensor-core path) */
 #define TYR_ATTN_ERR_ALIGN 4       /* pointer or stride breaks the 16-byte rule */
 #define TYR_ATTN_ERR_DTYPE 5       /* dtype/check_mode combination not supported */
@@ -62,6 +62,10 @@ extern "C" {
  * `is_causal` masks key j for query i when j > i (top-left aligned, as ATen and
  * cc/src/tyr.cpp:3990-3991).  LSE is the natural log of the sum of exp of the
  * SCALED scores (Tyr/GPU/Codegen/Macros.lean:155-163).
+ * Zero extents are treated as ATen's operator treats them: with batch, n_head
+ * or q_seq zero the output has no element and the call returns 0 without a
+ * launch (pointers may be NULL); with kv_seq zero every output row is 0 and
+ * its LSE -inf.
  * ---------------------------------------------------------------------- */
 typedef struct TyrAttnPrefillArgs {
   const void* q; /* [batch, n_head,    q_seq,  head_dim] */

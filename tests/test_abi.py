@@ -76,6 +76,37 @@ def test_arguments_are_rejected_before_any_launch(built_lib):
     assert built_lib.tyr_b200_attn_merge(None, None, None, None, None, None, 1, 64, None) == -1
 
 
+def test_zero_extents_follow_aten(built_lib):
+    # an output without elements: nothing to do, NULL pointers allowed
+    a = _lib.PrefillArgs()
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = 0, 4, 2, 16, 16, 64
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == 0
+    a.batch, a.q_seq = 2, 0
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == 0
+    assert built_lib.tyr_b200_attn_prefill_host(ctypes.byref(a), 0) == 0
+    a.q_seq, a.kv_seq = -1, 0
+    assert built_lib.tyr_b200_attn_prefill(ctypes.byref(a), None) == -1         # a negative extent is still refused
+    d = _lib.DecodeArgs()
+    d.n_head, d.n_kv_head, d.head_dim = 4, 2, 64
+    assert built_lib.tyr_b200_attn_decode(ctypes.byref(d), None) == 0           # no sequence
+    # no keys: the host-buffer call writes O = 0 and LSE = -inf itself, as ATen's operator returns them
+    import numpy as np
+    import torch
+    B, H, S, D = 2, 4, 3, 64
+    o = np.full((B, H, S, D), 0x7fc0, dtype=np.uint16)                             # bf16 NaN bits
+    lse = np.zeros((B, H, S), dtype=np.float32)
+    a = _lib.PrefillArgs()
+    a.o, a.lse = o.ctypes.data, lse.ctypes.data
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = B, H, 2, S, 0, D
+    a.o_stride[:] = [H * S * D, S * D, D]
+    a.dtype = _lib.TYR_ATTN_BF16
+    assert built_lib.tyr_b200_attn_prefill_host(ctypes.byref(a), 0) == 0
+    assert not o.any() and np.isneginf(lse).all()
+    ref = torch.nn.functional.scaled_dot_product_attention(torch.randn(B, H, S, D), torch.randn(B, H, 0, D),
+                                                           torch.randn(B, H, 0, D))
+    assert not ref.any()
+
+
 def test_prologue_limits_are_checked_on_the_host(built_lib):
     a = _lib.PrologueArgs()
     assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -1     # NULL pointers

@@ -390,3 +390,20 @@ def test_launches_are_counted():
     q = randn(1, 1, 64, 64).to(DEV)
     tnn.attentionFwd(q, q, q)
     assert tnn.launch_count() == n0 + 1
+
+
+def test_zero_extents_follow_aten():
+    # ATen's operator on the same shapes: an empty output for an empty batch / query, zeros without keys
+    for shape_q, shape_k in (((0, 4, 16, 64), (0, 2, 16, 64)), ((2, 4, 0, 64), (2, 2, 16, 64))):
+        q, k = torch.empty(shape_q, dtype=torch.bfloat16, device=DEV), randn(*shape_k).to(DEV) if shape_k[0] else \
+            torch.empty(shape_k, dtype=torch.bfloat16, device=DEV)
+        o, lse = tnn.attentionFwd(q, k, k, is_causal=False)
+        assert tuple(o.shape) == shape_q and tuple(lse.shape) == shape_q[:3]
+    q = randn(2, 4, 5, 128).to(DEV)
+    k = torch.empty(2, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
+    base = torch.full((2, 5, 4, 128), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = base.transpose(1, 2)                      # a strided output view
+    o, lse = tnn.attentionFwd(q, k, k, is_causal=False, out=out)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float().cpu(), k.float().cpu(), k.float().cpu(), enable_gqa=True)
+    assert torch.equal(o.float().cpu(), ref) and not ref.any()
+    assert torch.isneginf(lse).all()

@@ -51,6 +51,38 @@ int current_device_checked(int* dev) {
   return 0;
 }
 
+// A call with a zero extent, as ATen's operator treats it: an output without elements is nothing
+// to do, and attention over no keys is O = 0 (softmax over an empty row times an empty V).
+// 1: nothing to do; 2: no keys; 0: an ordinary call (or one the checks will refuse).
+int empty_kind(const TyrAttnPrefillArgs* a) {
+  if (!a || a->batch < 0 || a->n_head < 0 || a->n_kv_head < 0 || a->q_seq < 0 || a->kv_seq < 0 || a->head_dim <= 0) return 0;
+  if (a->batch == 0 || a->n_head == 0 || a->q_seq == 0) return 1;
+  if (a->kv_seq == 0 && a->o && (a->dtype == TYR_ATTN_BF16 || a->dtype == TYR_ATTN_F32)) return 2;
+  return 0;
+}
+
+// O = 0 and LSE = -inf for every query row: one thread per (row, 8 bytes of it)
+__global__ void no_keys_kernel(const TyrAttnPrefillArgs a, int esize) {
+  const int64_t per_row = (int64_t)a.head_dim * esize / 2;  // 2-byte units of a row
+  const int64_t rows = (int64_t)a.batch * a.n_head * a.q_seq;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * per_row) return;
+  const int64_t row = i / per_row, c = i - row * per_row;
+  const int64_t s = row % a.q_seq, h = (row / a.q_seq) % a.n_head, b = row / ((int64_t)a.q_seq * a.n_head);
+  uint16_t* o = static_cast<uint16_t*>(a.o) + (b * a.o_stride[0] + h * a.o_stride[1] + s * a.o_stride[2]) * (esize / 2);
+  o[c] = 0;
+  if (c == 0 && a.lse) a.lse[row] = -INFINITY;
+}
+
+int launch_no_keys(const TyrAttnPrefillArgs& a, cudaStream_t st) {
+  const int esize = a.dtype == TYR_ATTN_F32 ? 4 : 2;
+  const int64_t n = (int64_t)a.batch * a.n_head * a.q_seq * a.head_dim * esize / 2;
+  if (n > 0x7fffffffLL * 256) return -TYR_ATTN_ERR_TOO_LARGE;
+  no_keys_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, esize);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
 int check_prefill(const TyrAttnPrefillArgs* a) {
   if (!a || !a->q || !a->k || !a->v || !a->o) return -TYR_ATTN_ERR_NULL;
   if (a->batch <= 0 || a->n_head <= 0 || a->n_kv_head <= 0 || a->q_seq <= 0 || a->kv_seq <= 0 ||
@@ -146,6 +178,7 @@ using namespace tyr;
 extern "C" {
 
 int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* a, void* stream) {
+  if (const int kind = empty_kind(a)) return kind == 1 ? 0 : launch_no_keys(*a, static_cast<cudaStream_t>(stream));
   int rc = check_prefill(a);
   if (rc) return rc;
   const float scale = resolve_scale(a->scale, a->head_dim);
@@ -209,6 +242,7 @@ size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32
 }
 
 int tyr_b200_attn_decode(const TyrAttnDecodeArgs* a, void* stream) {
+  if (a && a->batch == 0 && a->n_head >= 0 && a->n_kv_head >= 0 && a->head_dim > 0) return 0;  // no sequence: nothing to do
   if (!a || !a->q || !a->o) return -TYR_ATTN_ERR_NULL;
   const bool ragged = a->k_ptrs != nullptr || a->v_ptrs != nullptr;
   if (ragged ? (!a->k_ptrs || !a->v_ptrs) : (!a->k || !a->v)) return -TYR_ATTN_ERR_NULL;
@@ -311,6 +345,19 @@ int64_t tyr_b200_attn_prefill_workspace_bytes(const TyrAttnPrefillArgs* a) {
 }
 
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
+  if (const int kind = empty_kind(a)) {
+    if (kind == 2) {  // no keys: the host output rows are zeros, their LSE -inf
+      const size_t row_bytes = (size_t)a->head_dim * (a->dtype == TYR_ATTN_F32 ? 4 : 2);
+      for (int64_t b = 0; b < a->batch; ++b)
+        for (int64_t h = 0; h < a->n_head; ++h)
+          for (int64_t r = 0; r < a->q_seq; ++r) {
+            const int64_t off = b * a->o_stride[0] + h * a->o_stride[1] + r * a->o_stride[2];
+            std::memset(static_cast<char*>(a->o) + off * (int64_t)(row_bytes / a->head_dim), 0, row_bytes);
+            if (a->lse) a->lse[(b * a->n_head + h) * a->q_seq + r] = -INFINITY;
+          }
+    }
+    return 0;
+  }
   int rc = check_prefill(a);
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment
   if (device < 0 || device >= kMaxDevices) return -TYR_ATTN_ERR_NO_DEVICE;
