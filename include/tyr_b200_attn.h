@@ -333,7 +333,8 @@ int tyr_b200_attn_backward(const TyrAttnBackwardArgs* args, void* stream);
  * the call a Tyr build makes when its tensors live on the CPU, which is the
  * only place the reference's CI ever runs attention
  * (.github/workflows/ci.yml:12-17).  Device staging buffers are cached per
- * device and grown on demand.  Tensors must be contiguous.
+ * device and grown on demand.  Tensors must be contiguous (strides that say
+ * otherwise are refused with TYR_ATTN_ERR_SHAPE); no padding mask.
  * ---------------------------------------------------------------------- */
 int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* args, int32_t device);
 

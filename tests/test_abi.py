@@ -107,6 +107,23 @@ def test_zero_extents_follow_aten(built_lib):
     assert not ref.any()
 
 
+def test_host_call_refuses_strided_tensors(built_lib):
+    buf = ctypes.create_string_buffer(1 << 16)
+    p = ctypes.addressof(buf)
+    a = _lib.PrefillArgs()
+    a.q = a.k = a.v = a.o = p
+    a.batch, a.n_head, a.n_kv_head, a.q_seq, a.kv_seq, a.head_dim = 2, 2, 2, 4, 4, 64
+    a.dtype = _lib.TYR_ATTN_BF16
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        getattr(a, name)[:] = [2 * 4 * 64, 4 * 64, 64]
+    a.o_stride[:] = [2 * 4 * 64, 64, 2 * 64]                                     # a [batch, seq, heads, dim] view
+    assert built_lib.tyr_b200_attn_prefill_host(ctypes.byref(a), 0) == -2
+    a.o_stride[:] = [2 * 4 * 64, 4 * 64, 64]
+    a.k_stride[:] = [2 * 8 * 64, 8 * 64, 64]                                     # a window of a longer cache
+    assert built_lib.tyr_b200_attn_prefill_host(ctypes.byref(a), 0) == -2
+    assert built_lib.tyr_b200_attn_prefill_host(ctypes.byref(a), 64) == -8       # device index out of range
+
+
 def test_prologue_limits_are_checked_on_the_host(built_lib):
     a = _lib.PrologueArgs()
     assert built_lib.tyr_b200_attn_qk_prologue(ctypes.byref(a), None) == -1     # NULL pointers

@@ -9,6 +9,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 
 #include "attn_internal.h"
@@ -362,6 +363,19 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   if (rc && rc != -TYR_ATTN_ERR_ALIGN) return rc;  // host pointers need no 16-byte alignment
   if (device < 0 || device >= kMaxDevices) return -TYR_ATTN_ERR_NO_DEVICE;
   if (a->key_mask) return -TYR_ATTN_ERR_DTYPE;  // the host-buffer call takes no padding mask
+  {
+    // the pieces below are cut out of contiguous [batch, heads, seq, head_dim] storage
+    const int64_t* strides[4] = {a->q_stride, a->k_stride, a->v_stride, a->o_stride};
+    const int64_t heads[4] = {a->n_head, a->n_kv_head, a->n_kv_head, a->n_head};
+    const int64_t seqs[4] = {a->q_seq, a->kv_seq, a->kv_seq, a->q_seq};
+    for (int t = 0; t < 4; ++t) {
+      int64_t want[3];
+      contiguous_strides(want, heads[t], seqs[t], a->head_dim);
+      const int64_t extent[3] = {a->batch, heads[t], seqs[t]};
+      for (int i = 0; i < 3; ++i)
+        if (extent[i] > 1 && strides[t][i] != want[i]) return -TYR_ATTN_ERR_SHAPE;
+    }
+  }
   const size_t es = a->dtype == TYR_ATTN_F32 ? 4 : 2;
   const size_t nq = (size_t)a->batch * a->n_head * a->q_seq * a->head_dim;
   const size_t nk = (size_t)a->batch * a->n_kv_head * a->kv_seq * a->head_dim;
@@ -376,7 +390,13 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   if ((e = cudaSetDevice(device)) != cudaSuccess) return (int)e;
   std::lock_guard<std::mutex> lock(g_host_mu);  // one host-buffer call per process at a time
   HostStage& hs = g_stage[device];
-  auto fail = [&](int code) { cudaSetDevice(prev); return code; };
+  // every way out drains the three streams first: the caller's host buffers are theirs again on return
+  auto fail = [&](int code) {
+    for (cudaStream_t s : {hs.out_stream, hs.compute, hs.stream})
+      if (s) cudaStreamSynchronize(s);
+    cudaSetDevice(prev);
+    return code;
+  };
   if (!hs.stream && (e = cudaStreamCreateWithFlags(&hs.stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail((int)e);
   if (hs.bytes < total) {
@@ -481,7 +501,8 @@ int tyr_b200_attn_prefill_host(const TyrAttnPrefillArgs* a, int32_t device) {
   e = cudaStreamSynchronize(so);
   if (e == cudaSuccess) e = cudaStreamSynchronize(sc);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-  return fail((int)e);
+  cudaSetDevice(prev);
+  return (int)e;
 }
 
 int tyr_b200_attn_device_status(int32_t device, int32_t clear) {

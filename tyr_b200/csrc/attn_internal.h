@@ -15,6 +15,7 @@ struct DeviceState {
 };
 DeviceState* device_state(int device);  // lazily created; nullptr on failure
 void count_launch(int n = 1);
+int sm_count();  // SMs of the current device (148 when it cannot be asked)
 // Cycles a single in-kernel barrier wait may take before its CTA gives up (api.cu; the default
 // unless a test shortened it).
 long long wait_limit_cycles();

@@ -393,17 +393,7 @@ int decode_num_splits(int max_kv_seq, int max_splits, int* chunk_len) {
 int decode_launch_splits(int max_kv_seq, int max_splits, long long ctas_per_chunk_index, int* chunk_len) {
   int cap_chunk = 0;
   decode_num_splits(max_kv_seq, max_splits, &cap_chunk);
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) {
-    static int cache[64] = {0};
-    if (dev >= 0 && dev < 64 && cache[dev] > 0) {
-      sms = cache[dev];
-    } else if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
-      if (dev >= 0 && dev < 64) cache[dev] = sms;
-    } else {
-      sms = 148;
-    }
-  }
+  const int sms = sm_count();
   const long long want = 4ll * 2 * sms;  // two CTAs are resident per SM
   int chunk = 2048;
   while (chunk > cap_chunk && ctas_per_chunk_index * ((max_kv_seq + chunk - 1) / chunk) < want) chunk /= 2;

@@ -37,6 +37,17 @@
 #include "ptx_sm100.cuh"
 
 namespace tyr {
+
+// SMs of the current device (the prefill kernels run one persistent CTA on each)
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  static std::atomic<int> cache[64] = {};
+  if (dev >= 0 && dev < 64 && (n = cache[dev].load(std::memory_order_relaxed)) > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
 namespace {
 
 constexpr int kBM = 128;        // query rows per tile (= TMEM lanes)
@@ -941,16 +952,6 @@ __global__ void __launch_bounds__(256) prefill_split_merge_kernel(const PrefillP
   if (col == 0 && p.lse != nullptr) p.lse[im.b * p.lse_stride_b + hq * p.lse_stride_h + row] = m + __logf(wsum);
 }
 
-// SMs of the current device (one persistent CTA each)
-int sm_count() {
-  int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  static std::atomic<int> cache[64] = {};
-  if (dev >= 0 && dev < 64 && (n = cache[dev].load(std::memory_order_relaxed)) > 0) return n;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
-  return n;
-}
 
 // Item tables of the tabled schedule, one per (device, launch geometry), built on first use and kept:
 // a few KB of device memory each, at most kMaxItemTables of them (further geometries run the static
