@@ -240,6 +240,22 @@ def test_strided_views_and_caller_allocated_outputs():
     assert_parity(ob.transpose(1, 2), None, ro, None)
 
 
+@pytest.mark.parametrize("B,H,Hkv,S,D,causal", [(2, 6, 3, 777, 64, True), (1, 8, 2, 2048, 128, False),
+                                                (3, 4, 4, 300, 128, True), (2, 15, 5, 1024, 64, False)])
+def test_layout_does_not_change_a_bit(B, H, Hkv, S, D, causal):
+    # [B,S,H,D] storage viewed as [B,H,S,D] against contiguous copies of the same values: the
+    # kernels see the same tiles either way, so O and LSE must agree bit for bit
+    q = randn(B, S, H, D, seed=61).to(DEV).transpose(1, 2)
+    k, v = randn(B, S, Hkv, D, seed=62).to(DEV).transpose(1, 2), randn(B, S, Hkv, D, seed=63).to(DEV).transpose(1, 2)
+    o1, l1 = tnn.attentionFwd(q, k, v, is_causal=causal)
+    ob = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=DEV)
+    o2, l2 = tnn.attentionFwd(q.contiguous(), k.contiguous(), v.contiguous(), is_causal=causal, out=ob.transpose(1, 2))
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    oc, lc = tnn.attentionFwd(q, k, v, is_causal=causal, check_mode=True)
+    oc2, lc2 = tnn.attentionFwd(q.contiguous(), k.contiguous(), v.contiguous(), is_causal=causal, check_mode=True)
+    assert torch.equal(oc, oc2) and torch.equal(lc, lc2)
+
+
 def test_rows_outside_the_tensor_are_not_written():
     S = 130
     q, k, v = randn(1, 2, S, 128, seed=31), randn(1, 2, S, 128, seed=32), randn(1, 2, S, 128, seed=33)
