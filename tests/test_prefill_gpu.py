@@ -423,3 +423,42 @@ def test_zero_extents_follow_aten():
     ref = torch.nn.functional.scaled_dot_product_attention(q.float().cpu(), k.float().cpu(), k.float().cpu(), enable_gqa=True)
     assert torch.equal(o.float().cpu(), ref) and not ref.any()
     assert torch.isneginf(lse).all()
+
+
+def test_calls_from_several_threads_on_their_own_streams():
+    # Lean may call from any task thread (no global state in the reference's entry points): three threads,
+    # each on its own stream; two of them meet a geometry that builds a schedule table on first use
+    # (causal, K/V beyond the L2 budget), at the same time
+    import threading
+    shapes = [((5, 8, 8192, 128), (5, 8, 8192, 128), True), ((3, 12, 6144, 128), (3, 12, 6144, 128), True),
+              ((2, 4, 700, 64), (2, 4, 700, 64), False)]
+    inputs = [(randn(*sq, seed=70 + i).to(DEV), randn(*sk, seed=80 + i).to(DEV), randn(*sk, seed=90 + i).to(DEV), c)
+              for i, (sq, sk, c) in enumerate(shapes)]
+    got, errs = [None] * len(shapes), []
+
+    def work(i):
+        try:
+            q, k, v, c = inputs[i]
+            st = torch.cuda.Stream(device=DEV)
+            with torch.cuda.stream(st):
+                for _ in range(20):
+                    o, lse = tnn.attentionFwd(q, k, v, is_causal=c)
+                st.synchronize()
+            got[i] = (o, lse)
+        except Exception as e:  # surfaced below: an exception in a thread would otherwise pass silently
+            errs.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errs, errs
+    torch.cuda.synchronize()
+    for (o, lse), (q, k, v, c) in zip(got, inputs):
+        wo, wl = tnn.attentionFwd(q, k, v, is_causal=c)
+        assert torch.equal(o, wo) and torch.equal(lse, wl)
+    # and against the oracle on one (batch, head) of the first
+    q, k, v, _ = inputs[0]
+    ro, rl = oracle(q[4:5, 7:8, :1024].cpu(), k[4:5, 7:8, :1024].cpu(), v[4:5, 7:8, :1024].cpu(), True)
+    assert_parity(got[0][0][4:5, 7:8, :1024], got[0][1][4:5, 7:8, :1024], ro, rl)
