@@ -188,3 +188,62 @@ def test_query_of_a_decode_step_is_rotated_at_its_position_and_stored_at_row_zer
     tnn.qkPrologue(x.to(DEV), out, w.to(DEV), cos.to(DEV), sin.to(DEV), positions=pos.to(DEV), out_at_row0=True)
     close(out, ref)
     assert tnn.device_status(0, True) == 0
+
+
+def test_token_loop_captured_in_a_cuda_graph():
+    """The decode step above as a serving loop would run it: the three prologue launches, the length
+    update and the decode launch captured once into a CUDA graph and replayed per token, with the
+    per-sequence lengths living on the device.  Every replay must give the bits of the same step run
+    eagerly, and the last one is checked against the oracle."""
+    g = torch.Generator(device="cpu").manual_seed(5)
+    B, Hq, Hkv, D, cap, steps = 2, 8, 2, 128, 4400, 4
+    start = [3, 4200]                                    # one sequence in a single chunk, one split over chunks
+    kc = torch.randn(B, Hkv, cap, D, generator=g).bfloat16().to(DEV)
+    vc = torch.randn(B, Hkv, cap, D, generator=g).bfloat16().to(DEV)
+    toks = [[torch.randn(B, 1, h, D, generator=g).bfloat16().to(DEV) for h in (Hq, Hkv, Hkv)] for _ in range(steps)]
+    qn, kn = (torch.rand(D, generator=g) + 0.5).to(DEV), (torch.rand(D, generator=g) + 0.5).to(DEV)
+    cos, sin = (t.to(DEV) for t in rope_tables(cap, D))
+    ws = torch.empty(tnn._lib.load().tyr_b200_attn_decode_workspace_bytes(B, Hq, D, cap, 64), dtype=torch.uint8, device=DEV)
+
+    def step(q_in, k_in, v_in, kcache, vcache, lens, lens_next, qd):
+        tnn.qkPrologue(k_in, kcache, kn, cos, sin, positions=lens)
+        tnn.qkPrologue(v_in, vcache, positions=lens)
+        tnn.qkPrologue(q_in, qd, qn, cos, sin, positions=lens, out_at_row0=True)
+        torch.add(lens, 1, out=lens_next)
+        o, lse = tnn.flashDecodeDense(qd, kcache, vcache, kv_lens=lens_next, kv_len=cap, workspace=ws)
+        lens.copy_(lens_next)
+        return o, lse
+
+    # eager run on copies of the caches
+    ke, ve = kc.clone(), vc.clone()
+    lens_e = torch.tensor(start, dtype=torch.int32, device=DEV)
+    nxt_e, qd_e = torch.empty_like(lens_e), torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    eager = []
+    for q_in, k_in, v_in in toks:
+        o, lse = step(q_in, k_in, v_in, ke, ve, lens_e, nxt_e, qd_e)
+        eager.append((o.clone(), lse.clone()))
+    # captured run: static input buffers, one capture, one replay per token
+    kg, vg = kc.clone(), vc.clone()
+    lens_g = torch.tensor(start, dtype=torch.int32, device=DEV)
+    nxt_g, qd_g = torch.empty_like(lens_g), torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    q_s, k_s, v_s = (torch.empty_like(t) for t in toks[0])
+    tnn.flashDecodeDense(qd_g.zero_(), kg, vg, kv_len=1, workspace=ws)      # loads the kernels outside the capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            o_g, lse_g = step(q_s, k_s, v_s, kg, vg, lens_g, nxt_g, qd_g)
+    for (q_in, k_in, v_in), (oe, le) in zip(toks, eager):
+        q_s.copy_(q_in); k_s.copy_(k_in); v_s.copy_(v_in)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(o_g, oe) and torch.equal(lse_g, le)
+    assert torch.equal(kg, ke) and torch.equal(vg, ve) and lens_g.tolist() == [s + steps for s in start]
+    assert tnn.device_status(0, True) == 0
+    # the last token against the oracle, sequence by sequence
+    for b, s0 in enumerate(start):
+        L = s0 + steps
+        ro, _ = c_oracle.sdpa(qd_g[b:b + 1].float().cpu().numpy(), kg[b:b + 1, :, :L].float().cpu().numpy(),
+                              vg[b:b + 1, :, :L].float().cpu().numpy(), False)
+        assert np.abs(o_g[b].float().cpu().numpy() - ro[0, :, 0]).max() <= 2e-2
