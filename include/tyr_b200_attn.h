@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define TYR_ATTN_ABI_VERSION 7
+#define TYR_ATTN_ABI_VERSION 8
 
 /* element types of Q/K/V/O */
 #define TYR_ATTN_BF16 0
@@ -184,6 +184,9 @@ typedef struct TyrAttnDecodeArgs {
   int32_t max_splits; /* 0 => 64; clamped to [1,64] */
   void* workspace;    /* device scratch, >= tyr_b200_attn_decode_workspace_bytes() */
   size_t workspace_bytes;
+  int64_t total_kv_len; /* sum of the sequences' lengths when the host knows it, else 0.  Only steers the
+                           chunk length of the launch (a small launch is cut into one wave of CTAs);
+                           results do not depend on it */
 } TyrAttnDecodeArgs;
 
 size_t tyr_b200_attn_decode_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim,

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(built_lib):
 
 
 def test_abi_version_and_error_strings(built_lib):
-    assert built_lib.tyr_b200_attn_abi_version() == 7
+    assert built_lib.tyr_b200_attn_abi_version() == 8
     assert built_lib.tyr_b200_attn_strerror(0) == b"ok"
     for code in range(1, 12):
         assert built_lib.tyr_b200_attn_strerror(-code).startswith(b"tyr_b200_attn:")
@@ -35,7 +35,7 @@ def test_abi_version_and_error_strings(built_lib):
 def test_struct_sizes_match_the_c_layout():
     # 5 pointers, 6 int32, 12 int64, int32 int32 float int32 int32 (+4 padding), pointer, int64, pointer, int64
     assert ctypes.sizeof(_lib.PrefillArgs) == 5 * 8 + 6 * 4 + 12 * 8 + 5 * 4 + 4 + 8 + 8 + 8 + 8
-    assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8
+    assert ctypes.sizeof(_lib.DecodeArgs) == 9 * 8 + 5 * 4 + 4 + 10 * 8 + 4 + 4 + 8 + 8 + 8
     # 10 pointers, uint64, 6 int32, 24 int64, int32 int32 float int32, pointer, int64
     assert ctypes.sizeof(_lib.BackwardArgs) == 10 * 8 + 8 + 6 * 4 + 24 * 8 + 4 * 4 + 8 + 8
     # 6 pointers, 5 int32 (+4 padding), 6 int64, float int32 int32 (+4 padding), pointer, int64, int32 (+4)

@@ -53,6 +53,24 @@ def test_split_count_does_not_change_the_answer(max_splits):
         check_seq(q[b], ks[b], vs[b], o[b], lse[b], (max_splits, b))
 
 
+@pytest.mark.parametrize("lens", [[9000], [4100, 300, 7000], [2500] * 6])
+def test_length_hint_only_steers_the_chunks(lens):
+    # total_kv_len (the sum the host knows) lets a small launch cut its chunks for one wave of CTAs;
+    # without it, or with a sum that cannot be right, the answer stays within the same bars
+    Hq, Hkv, D = 8, 2, 128
+    ks = [randn(Hkv, L, D, seed=L).to(DEV) for L in lens]
+    vs = [randn(Hkv, L, D, seed=L + 3).to(DEV) for L in lens]
+    q = randn(len(lens), Hq, D, seed=5).to(DEV)
+    plan = tnn.DecodePlan(ks, vs, Hq)
+    assert plan.total_kv_len == sum(lens)
+    for hint in (sum(lens), 0, 1, 10 ** 12):
+        plan.total_kv_len = hint
+        o, lse = tnn.flashDecode(q, plan)
+        for b in range(len(lens)):
+            check_seq(q[b], ks[b], vs[b], o[b], lse[b], f"hint {hint} seq {b}")
+    assert tnn.device_status(0, True) == 0
+
+
 def test_dense_cache_layout_and_4d_query():
     # Tyr's KVCache: [batch, n_kv_head, maxLen, head_dim] with a shared `seq` counter
     B, Hq, Hkv, cap, D, kv_len = 3, 8, 2, 1024, 128, 777

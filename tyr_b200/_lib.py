@@ -52,6 +52,7 @@ class DecodeArgs(ctypes.Structure):
         ("q_stride", c_i64 * 2), ("o_stride", c_i64 * 2), ("k_stride", c_i64 * 3),
         ("v_stride", c_i64 * 3),
         ("scale", c_f32), ("max_splits", c_i32), ("workspace", vp), ("workspace_bytes", ctypes.c_size_t),
+        ("total_kv_len", c_i64),
     ]
 
 

@@ -386,17 +386,43 @@ int decode_num_splits(int max_kv_seq, int max_splits, int* chunk_len) {
 
 // Chunk length of a launch.  decode_num_splits gives the most chunks the workspace is sized for;
 // a launch uses longer chunks than that when it can: every CTA pays for filling its load pipeline,
-// the cross-warp merge and a partial output row, and 2048-key chunks instead of 512-key ones
-// measured 5.9 -> 6.95 TB/s on 64 sequences of up to 32 K keys (24 or 32 chunks per sequence within
-// 2-4 % of that; 8 sequences: best at 32 chunks, 5.34 -> 5.77 TB/s).  Shorter chunks only while the
-// launch would otherwise have fewer than four CTAs for every CTA slot of the device.
-int decode_launch_splits(int max_kv_seq, int max_splits, long long ctas_per_chunk_index, int* chunk_len) {
+// the cross-warp merge and a partial output row.
+//  * A launch with at least four CTAs for every CTA slot of the device at 2048-key chunks takes
+//    those (64 sequences of up to 32 K keys: 5.9 -> 6.95 TB/s against 512-key chunks).
+//  * A launch of fewer than three CTAs per slot at 2048-key chunks whose lengths the host knows (one
+//    shared length, or the caller's total_kv_len) takes the shortest chunks that still fit in ONE
+//    wave of CTAs, all resident at once: each pays its start-up once and none waits for a slot
+//    (one sequence of 32 K keys: 37.1 -> 31.3 us; 4 x 32 K: 106 -> 86 us; 8 x 8 K: 66 -> 53 us;
+//    eight ragged sequences of up to 32 K, 2.8 CTAs per slot: 149 -> 134 us; 8 x 32 K, 3.5 CTAs per
+//    slot, lost 4 % that way and stays with the rule below).
+//  * Any other launch halves the chunks from 2048 keys down while it would have fewer than four CTAs
+//    per slot (by the longest sequence's count when the lengths are only on the device: ragged
+//    lengths leave about half of those with work).
+int decode_launch_splits(int max_kv_seq, int max_splits, int batch, int ctas_per_seq_chunk, long long total_kv_len,
+                         bool lengths_known, int* chunk_len) {
   int cap_chunk = 0;
   decode_num_splits(max_kv_seq, max_splits, &cap_chunk);
-  const int sms = sm_count();
-  const long long want = 4ll * 2 * sms;  // two CTAs are resident per SM
+  total_kv_len = std::min<long long>(total_kv_len, (long long)batch * max_kv_seq);  // a hint, not trusted beyond the shapes
+  const long long slots = 2ll * sm_count();  // two CTAs are resident per SM
+  // CTAs that find work with chunks of `chunk` keys
+  auto ctas = [&](int chunk) -> long long {
+    if (total_kv_len > 0) return ctas_per_seq_chunk * (total_kv_len / chunk + (batch + 1) / 2);
+    return (long long)ctas_per_seq_chunk * batch * ((max_kv_seq + chunk - 1) / chunk);
+  };
+  const int whole = (max_kv_seq + kTileKeys - 1) / kTileKeys * kTileKeys;  // one chunk per sequence
   int chunk = 2048;
-  while (chunk > cap_chunk && ctas_per_chunk_index * ((max_kv_seq + chunk - 1) / chunk) < want) chunk /= 2;
+  if (ctas(chunk) < 4 * slots) {
+    if (lengths_known && ctas(chunk) < 3 * slots) {
+      const long long keys = total_kv_len > 0 ? total_kv_len : (long long)batch * max_kv_seq;
+      long long c = (keys * ctas_per_seq_chunk + slots - 1) / slots;
+      c = (c + kTileKeys - 1) / kTileKeys * kTileKeys;
+      c = std::max<long long>(c, kMinChunk);
+      while (c < whole && ctas((int)c) > slots) c += kTileKeys;
+      chunk = (int)std::min<long long>(c, whole);
+    } else {
+      while (chunk > cap_chunk && ctas(chunk) < 4 * slots) chunk /= 2;
+    }
+  }
   if (chunk < cap_chunk) chunk = cap_chunk;  // never more chunks than the workspace holds
   *chunk_len = chunk;
   return (max_kv_seq + chunk - 1) / chunk;
@@ -425,7 +451,8 @@ int launch_decode(const TyrAttnDecodeArgs& a, float scale, cudaStream_t st) {
   for (int i = 0; i < 2; ++i) { p.qs[i] = a.q_stride[i]; p.os[i] = a.o_stride[i]; }
   for (int i = 0; i < 3; ++i) { p.ks[i] = a.k_stride[i]; p.vs[i] = a.v_stride[i]; }
   p.scale_log2 = scale * kLog2e;
-  p.n_splits = decode_launch_splits(a.max_kv_seq, a.max_splits, (long long)a.batch * a.n_kv_head * p.head_groups,
+  p.n_splits = decode_launch_splits(a.max_kv_seq, a.max_splits, a.batch, a.n_kv_head * p.head_groups,
+                                    a.total_kv_len > 0 ? a.total_kv_len : 0, a.kv_lens == nullptr || a.total_kv_len > 0,
                                     &p.chunk_len);
   p.ws_o = nullptr;
   p.ws_lse = nullptr;

@@ -286,6 +286,7 @@ class DecodePlan:
         self._keep = (list(k_list), list(v_list))
         self.max_kv_seq = max(lens)
         self.lens_host = lens
+        self.total_kv_len = int(sum(lens))
         self.kv_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
         self.k_ptrs = torch.tensor(kp, dtype=torch.int64, device=dev)
         self.v_ptrs = torch.tensor(vp, dtype=torch.int64, device=dev)
@@ -311,6 +312,7 @@ def _fill_decode(q3, plan: DecodePlan, out, lse, scale) -> DecodeArgs:
     a.k_stride[:] = [0, 0, plan.head_dim]
     a.v_stride[:] = [0, 0, plan.head_dim]
     a.scale, a.max_splits = float(scale or 0.0), plan.max_splits
+    a.total_kv_len = plan.total_kv_len     # the host built the plan from these lengths: let the launch size its chunks by them
     return a
 
 
@@ -399,6 +401,7 @@ def flashDecodeDense(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     a.k_stride[:] = [k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)]
     a.v_stride[:] = [v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)]
     a.scale, a.max_splits = float(scale or 0.0), max_splits
+    a.total_kv_len = 0                     # a shared length is known as it is; per-sequence lengths live on the device
     a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     with torch.cuda.device(q.device):
         check(L.tyr_b200_attn_decode(ctypes.byref(a), _stream_ptr(q)))
