@@ -412,13 +412,18 @@ int decode_launch_splits(int max_kv_seq, int max_splits, int batch, int ctas_per
   const int whole = (max_kv_seq + kTileKeys - 1) / kTileKeys * kTileKeys;  // one chunk per sequence
   int chunk = 2048;
   if (ctas(chunk) < 4 * slots) {
+    long long one_wave = 0;  // chunk length of the one-wave cut, 0 when the launch does not take it
     if (lengths_known && ctas(chunk) < 3 * slots) {
       const long long keys = total_kv_len > 0 ? total_kv_len : (long long)batch * max_kv_seq;
       long long c = (keys * ctas_per_seq_chunk + slots - 1) / slots;
       c = (c + kTileKeys - 1) / kTileKeys * kTileKeys;
-      c = std::max<long long>(c, kMinChunk);
+      c = std::min<long long>(std::max<long long>(c, kMinChunk), whole);
       while (c < whole && ctas((int)c) > slots) c += kTileKeys;
-      chunk = (int)std::min<long long>(c, whole);
+      // short sequences, many of them: even one CTA per (sequence, KV head) is more than a wave
+      if (ctas((int)c) <= slots) one_wave = c;
+    }
+    if (one_wave > 0) {
+      chunk = (int)one_wave;
     } else {
       while (chunk > cap_chunk && ctas(chunk) < 4 * slots) chunk /= 2;
     }
