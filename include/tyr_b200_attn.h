@@ -104,7 +104,8 @@ typedef struct TyrAttnPrefillArgs {
 int tyr_b200_attn_prefill(const TyrAttnPrefillArgs* args, void* stream);
 /* Bytes of `workspace` with which the call above would split its last round on the current
  * device; 0 when it would not split (causal, windowed or masked calls, short key sequences, a
- * last round that is more than half full), negative TYR_ATTN_ERR_* on bad arguments. */
+ * last round that is more than half full, more than eight full rounds before it), negative
+ * TYR_ATTN_ERR_* on bad arguments. */
 int64_t tyr_b200_attn_prefill_workspace_bytes(const TyrAttnPrefillArgs* args);
 
 /* Contiguous-layout forms whose argument lists mirror the Lean externs one to
