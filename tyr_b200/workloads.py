@@ -43,7 +43,7 @@ class Workload:
 
 
 WORKLOADS = {
-    # BASELINE configs[0..4]
+    # the five benchmarked shapes (name, kind, batch, query heads, KV heads, sequence, head_dim, causal, seed, normalised Q/K)
     "gpt_char": Workload("gpt_char", "prefill", 64, 6, 6, 256, 64, True, 0, False),
     "qwen3_0p6b_prefill": Workload("qwen3_0p6b_prefill", "prefill", 8, 16, 8, 2048, 128, True, 1, True),
     "qwen3_8b_prefill": Workload("qwen3_8b_prefill", "prefill", 4, 32, 8, 8192, 128, True, 2, True),
