@@ -327,6 +327,8 @@ typedef struct TyrAttnBackwardArgs {
   int64_t key_mask_stride;
 } TyrAttnBackwardArgs;
 
+/* Zero extents as autograd of ATen's operator treats them: without queries (batch, n_head or q_seq
+ * zero) dQ has no element and dK, dV are written as zeros; without keys dQ is written as zeros. */
 uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, int32_t q_seq);
 int tyr_b200_attn_backward(const TyrAttnBackwardArgs* args, void* stream);
 

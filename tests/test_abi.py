@@ -89,6 +89,13 @@ def test_zero_extents_follow_aten(built_lib):
     d = _lib.DecodeArgs()
     d.n_head, d.n_kv_head, d.head_dim = 4, 2, 64
     assert built_lib.tyr_b200_attn_decode(ctypes.byref(d), None) == 0           # no sequence
+    g = _lib.BackwardArgs()                                                      # gradients of an empty batch: nothing to write
+    g.n_head, g.n_kv_head, g.q_seq, g.kv_seq, g.head_dim = 4, 2, 16, 16, 64
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(g), None) == 0
+    g.batch, g.q_seq, g.kv_seq = 2, 0, 0                                         # neither queries nor keys
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(g), None) == 0
+    g.q_seq = 16                                                                 # no keys: dQ = 0 needs its pointer
+    assert built_lib.tyr_b200_attn_backward(ctypes.byref(g), None) == -1
     # no keys: the host-buffer call writes O = 0 and LSE = -inf itself, as ATen's operator returns them
     import numpy as np
     import torch

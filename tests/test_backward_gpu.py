@@ -272,3 +272,24 @@ def test_benchmark_shapes_by_sampled_key_blocks_and_rows(name):
             assert np.isfinite(gg).all(), (name, what, b, hkv, j0)
             err = np.abs(gg - want).max() / max(np.abs(want).max(), 1e-6)
             assert err <= GRAD_REL_TO_MAX, f"{name} {what} block (b={b}, kv head {hkv}, keys {j0}..): {err:.3e}"
+
+
+def test_zero_extents_follow_autograd():
+    # autograd of ATen's operator on the same shapes: no queries -> dK, dV are zeros; no keys -> dQ is zeros
+    from tyr_b200 import nn as tnn
+    dev = _dev()
+    q = torch.empty(2, 4, 0, 64, dtype=torch.bfloat16, device=dev)
+    k = torch.randn(2, 2, 33, 64, device=dev).bfloat16()
+    o, lse = tnn.attentionFwd(q, k, k, is_causal=False)
+    dq, dk, dv = tnn.attentionBwd(q, k, k, o, lse, torch.empty_like(q), is_causal=False)
+    assert dq.numel() == 0 and not dk.any() and not dv.any() and dk.shape == k.shape
+    q = torch.randn(2, 4, 5, 128, device=dev).bfloat16()
+    k = torch.empty(2, 2, 0, 128, dtype=torch.bfloat16, device=dev)
+    o, lse = tnn.attentionFwd(q, k, k, is_causal=False)
+    dq, dk, dv = tnn.attentionBwd(q, k, k, o, lse, torch.randn_like(q), is_causal=False)
+    assert not dq.any() and dq.shape == q.shape and dk.numel() == 0 and dv.numel() == 0
+    qf = q.float().cpu().requires_grad_(True)
+    kf = k.float().cpu().requires_grad_(True)
+    ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, kf, enable_gqa=True)
+    ref.backward(torch.ones_like(ref))
+    assert not qf.grad.any()

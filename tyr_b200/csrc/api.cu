@@ -62,26 +62,40 @@ int empty_kind(const TyrAttnPrefillArgs* a) {
   return 0;
 }
 
-// O = 0 and LSE = -inf for every query row: one thread per (row, 8 bytes of it)
-__global__ void no_keys_kernel(const TyrAttnPrefillArgs a, int esize) {
-  const int64_t per_row = (int64_t)a.head_dim * esize / 2;  // 2-byte units of a row
-  const int64_t rows = (int64_t)a.batch * a.n_head * a.q_seq;
+// Zeros into every row of a [batch, heads, seq, d] tensor with element strides (rows of d contiguous
+// elements of `esize` bytes), and -inf into `lse` [batch, heads, seq] when given: one thread per 2 bytes.
+struct ZeroRows {
+  void* base;
+  float* lse;
+  int64_t batch, heads, seq, d, stride[3];
+  int esize;
+};
+__global__ void zero_rows_kernel(const ZeroRows z) {
+  const int64_t per_row = z.d * z.esize / 2;  // 2-byte units of a row
+  const int64_t rows = z.batch * z.heads * z.seq;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * per_row) return;
   const int64_t row = i / per_row, c = i - row * per_row;
-  const int64_t s = row % a.q_seq, h = (row / a.q_seq) % a.n_head, b = row / ((int64_t)a.q_seq * a.n_head);
-  uint16_t* o = static_cast<uint16_t*>(a.o) + (b * a.o_stride[0] + h * a.o_stride[1] + s * a.o_stride[2]) * (esize / 2);
+  const int64_t s = row % z.seq, h = (row / z.seq) % z.heads, b = row / (z.seq * z.heads);
+  uint16_t* o = static_cast<uint16_t*>(z.base) + (b * z.stride[0] + h * z.stride[1] + s * z.stride[2]) * (z.esize / 2);
   o[c] = 0;
-  if (c == 0 && a.lse) a.lse[row] = -INFINITY;
+  if (c == 0 && z.lse) z.lse[row] = -INFINITY;
 }
 
-int launch_no_keys(const TyrAttnPrefillArgs& a, cudaStream_t st) {
-  const int esize = a.dtype == TYR_ATTN_F32 ? 4 : 2;
-  const int64_t n = (int64_t)a.batch * a.n_head * a.q_seq * a.head_dim * esize / 2;
+int launch_zero_rows(void* base, float* lse, int64_t batch, int64_t heads, int64_t seq, int64_t d, const int64_t* stride,
+                     int esize, cudaStream_t st) {
+  const int64_t n = batch * heads * seq * d * esize / 2;
+  if (n == 0) return 0;
   if (n > 0x7fffffffLL * 256) return -TYR_ATTN_ERR_TOO_LARGE;
-  no_keys_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, esize);
+  const ZeroRows z{base, lse, batch, heads, seq, d, {stride[0], stride[1], stride[2]}, esize};
+  zero_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(z);
   count_launch();
   return (int)cudaGetLastError();
+}
+
+// attention over no keys: O = 0 and LSE = -inf for every query row
+int launch_no_keys(const TyrAttnPrefillArgs& a, cudaStream_t st) {
+  return launch_zero_rows(a.o, a.lse, a.batch, a.n_head, a.q_seq, a.head_dim, a.o_stride, a.dtype == TYR_ATTN_F32 ? 4 : 2, st);
 }
 
 int check_prefill(const TyrAttnPrefillArgs* a) {
@@ -306,6 +320,23 @@ uint64_t tyr_b200_attn_backward_workspace_bytes(int32_t batch, int32_t n_head, i
 }
 
 int tyr_b200_attn_backward(const TyrAttnBackwardArgs* a, void* stream) {
+  // Zero extents as autograd of ATen's operator treats them: without queries (or heads, or a batch)
+  // dQ has no element and dK, dV are zeros; without keys dK, dV have no element and dQ is zeros.
+  if (a && a->batch >= 0 && a->n_head >= 0 && a->n_kv_head >= 0 && a->q_seq >= 0 && a->kv_seq >= 0 &&
+      a->dtype == TYR_ATTN_BF16 && (a->head_dim == 64 || a->head_dim == 128) &&
+      (a->batch == 0 || a->n_head == 0 || a->q_seq == 0 || a->kv_seq == 0)) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->batch == 0) return 0;
+    if (a->kv_seq == 0) {
+      if (a->n_head == 0 || a->q_seq == 0) return 0;
+      if (!a->d_q) return -TYR_ATTN_ERR_NULL;
+      return launch_zero_rows(a->d_q, nullptr, a->batch, a->n_head, a->q_seq, a->head_dim, a->dq_stride, 2, st);
+    }
+    if (a->n_kv_head == 0) return 0;
+    if (!a->d_k || !a->d_v) return -TYR_ATTN_ERR_NULL;
+    const int rc = launch_zero_rows(a->d_k, nullptr, a->batch, a->n_kv_head, a->kv_seq, a->head_dim, a->dk_stride, 2, st);
+    return rc ? rc : launch_zero_rows(a->d_v, nullptr, a->batch, a->n_kv_head, a->kv_seq, a->head_dim, a->dv_stride, 2, st);
+  }
   if (!a || !a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->d_q || !a->d_k || !a->d_v)
     return -TYR_ATTN_ERR_NULL;
   if (a->batch <= 0 || a->n_head <= 0 || a->n_kv_head <= 0 || a->q_seq <= 0 || a->kv_seq <= 0)
